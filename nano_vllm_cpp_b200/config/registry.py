@@ -1,5 +1,5 @@
-"""One registry from an architecture's name (``architectures[0]`` of config.json)
-to its configuration class and its model builder.
+"""One registry from an architecture's name (``architectures[0]`` of config.json, or its ``architecture``
+string) to its configuration class and its model builder.
 
 The reference has no such table: its runner owns one model class by value
 (include/nanovllm/model_runner.hpp:29) and never reads ``architectures``.
@@ -42,13 +42,21 @@ def get_architecture(name: str) -> Architecture:
 def load_model_config(model_dir: str):
     """Read ``config.json`` and return ``(architecture, typed config)``."""
     d = read_config_json(model_dir)
-    archs = d.get("architectures")
-    if not isinstance(archs, list) or not archs:
-        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names")
-    arch = get_architecture(archs[0])
+    arch = get_architecture(architecture_name(d))
     return arch, arch.config_from_dict(d)
 
 
+def architecture_name(d: dict) -> str:
+    """The model class a config.json names: the first of ``architectures``, or the string ``architecture``."""
+    archs = d.get("architectures")
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    if isinstance(d.get("architecture"), str):
+        return d["architecture"]
+    raise ConfigError("config.json: key 'architectures' must be a non-empty list of names "
+                      "(or 'architecture' a name)")
+
+
 def _ensure_builtin() -> None:
-    # The built-in architecture registers itself on import.
-    from ..models import qwen2_moe  # noqa: F401
+    # The built-in architectures register themselves on import.
+    from ..models import qwen2_moe, bizodra  # noqa: F401

@@ -695,6 +695,157 @@ def sample_nucleus(logits, params, recent, recent_off, out) -> None:
                                    _p(out), _stream()), "sample_nucleus")
 
 
+# ----------------------------------------------------------------------------- state mixers and their layer pieces
+ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def _f32(*ts) -> None:
+    for t in ts:
+        if t is not None:
+            _need(t.dtype == torch.float32, f"tensor must be float32, found {t.dtype}")
+
+
+def branch_norm_add(x, branches, weight, eps: float, out=None, *, branch_weights=None, mix_scale: float = 1.0) -> None:
+    """``x += rms(y) * weight`` row by row, and ``out`` (float32 or bfloat16, optional) = the new ``x``.
+    ``y`` is the one branch, or with ``branch_weights`` ``mix_scale * sum_b rms(branches[b]) * branch_weights[b]``.
+    ``rms(v) = v / sqrt(mean(v^2) + eps)``.  Without branches only ``out = x`` is written."""
+    branches = list(branches or [])
+    bws = list(branch_weights or [])
+    _cuda_contig(x, weight, out, *branches, *bws)
+    _f32(x, weight, *branches, *bws)
+    T, H = x.shape
+    _need(len(branches) <= 4 and (not bws or len(bws) == len(branches)), "branch_norm_add: up to four branches, a weight for each or for none")
+    _need(len(branches) <= 1 or bws, "branch_norm_add: several branches need their weights")
+    _need(not branches or (weight is not None and weight.numel() == H), "branch_norm_add: weight")
+    for b in branches:
+        _need(b.shape == x.shape, "branch_norm_add: a branch is shaped like x")
+    for w in bws:
+        _need(w.numel() == H, "branch_norm_add: a branch weight has one entry per column")
+    _need(out is None or out.shape == x.shape, "branch_norm_add: out shape")
+    b4 = branches + [None] * (4 - len(branches))
+    w4 = bws + [None] * (4 - len(bws))
+    _check(lib().nv_branch_norm_add(_p(x), _p(b4[0]), _p(b4[1]), _p(b4[2]), _p(b4[3]), _p(w4[0]), _p(w4[1]), _p(w4[2]),
+                                    _p(w4[3]), len(branches), mix_scale, _p(weight), eps, _p(out),
+                                    (dt(out) if out is not None else 0), T, H, _stream()), "branch_norm_add")
+
+
+def activation(src, out, kind: str) -> None:
+    """``out = act(src)`` elementwise; ``kind``: gelu_erf, gelu_tanh or silu."""
+    _cuda_contig(src, out)
+    _need(src.shape == out.shape and kind in ACTIVATIONS, "activation: shapes or kind")
+    _check(lib().nv_activation(_p(src), dt(src), _p(out), dt(out), src.numel(), ACTIVATIONS[kind], _stream()),
+           "activation")
+
+
+def token_gate(gate, ids, table, col0: int, out, err: ErrorFlag, feed=None) -> None:
+    """``out[t, j] = gelu_tanh(gate[t, j]) * table[ids[t], col0 + j]`` (negative ids point into ``feed``)."""
+    _cuda_contig(ids, table, out, feed)
+    _i32(ids, feed)
+    T, d = out.shape
+    _need(gate.stride(-1) == 1 and gate.shape[0] == T and gate.shape[1] >= d, "token_gate: gate rows")
+    _check(lib().nv_token_gate(_p(gate), dt(gate), gate.stride(0), _p(ids), _p(feed), _p(table), dt(table),
+                               table.stride(0), col0, d, table.shape[0], _p(out), dt(out), T, _p(err.t), _stream()),
+           "token_gate")
+
+
+def _slot_stride(state) -> int:
+    """Elements between two slots of a per-request state array (a slot's own elements are contiguous)."""
+    _need(state.is_cuda and state.dtype == torch.float32, "state arrays are float32 on the device")
+    inner = state[0]
+    _need(inner.is_contiguous(), "a slot of a state array must be contiguous")
+    return state.stride(0)
+
+
+def conv_silu_norm(src, col0: int, C: int, w, taps: int, batch, state, out, *, unit_heads: int = 0, unit_dim: int = 1,
+                   unit_eps: float = 0.0, scaled_heads: int = 0, scale: float = 1.0) -> None:
+    """Short causal convolution over time per channel (columns col0..col0+C of ``src``), then silu; the first
+    ``unit_heads`` heads of ``unit_dim`` channels become unit vectors (the first ``scaled_heads`` times ``scale``).
+    ``state`` [slots, taps - 1, C] holds what came before the rows of this step."""
+    _cuda_contig(w, out)
+    _f32(w, out)
+    T = src.shape[0]
+    _need(src.stride(-1) == 1 and out.shape == (T, C) and w.shape == (C, taps), "conv_silu_norm: shapes")
+    _check(lib().nv_conv_silu_norm(_p(src), dt(src), src.stride(0), col0, C, _p(w), taps, _p(batch.row_entry),
+                                   _p(batch.cu_rows), _p(batch.entry_slot), _p(state), _slot_stride(state),
+                                   unit_heads, unit_dim, unit_eps, scaled_heads, scale, _p(out), T, _stream()),
+           "conv_silu_norm")
+
+
+def conv_state_update(src, col0: int, C: int, taps: int, batch, state) -> None:
+    """After ``conv_silu_norm``: the last ``taps - 1`` inputs of every entry's channels go to its state."""
+    _check(lib().nv_conv_state_update(_p(src), dt(src), src.stride(0), col0, C, taps, _p(batch.cu_rows),
+                                      _p(batch.entry_slot), _p(state), _slot_stride(state), batch.S, _stream()),
+           "conv_state_update")
+
+
+def scan_usable(dk: int, dv: int, parts: int = 1) -> bool:
+    return bool(lib().nv_scan_usable(dk, dv, parts))
+
+
+def mlstm_scan(proj, cols: dict, batch, S, n, m, H: int, dk: int, dv: int, cap: float, eps: float, norm_w, out,
+               *, den_eps: float = 1e-6) -> None:
+    """The matrix memory with exponential gating, row by row per entry, from and to the entries' states.
+    ``proj`` float32 [T, P] holds q, k, v, the output gate and the two gate pre-activations at ``cols``
+    (keys q, k, v, g, i, f)."""
+    _cuda_contig(proj, norm_w, out)
+    _f32(proj, norm_w)
+    _need(norm_w.numel() in (dv, H * dv) and out.shape == (proj.shape[0], H * dv), "mlstm_scan: shapes")
+    _check(lib().nv_mlstm_scan(_p(proj), proj.stride(0), cols["q"], cols["k"], cols["v"], cols["g"], cols["i"],
+                               cols["f"], _p(batch.cu_rows), _p(batch.entry_slot), _p(S), _slot_stride(S), _p(n),
+                               _slot_stride(n), _p(m), _slot_stride(m), H, dk, dv, cap, float(dk) ** -0.5, den_eps,
+                               eps, _p(norm_w), (1 if norm_w.numel() == H * dv and H > 1 else 0), _p(out), dt(out),
+                               batch.S, _stream()), "mlstm_scan")
+
+
+def gated_delta_scan(qkv, cols: dict, G: int, proj, pcols: dict, A_log, dt_bias, batch, S, H: int, dk: int, dv: int,
+                     eps: float, norm_w, out) -> None:
+    """The gated delta rule, row by row per entry.  ``qkv`` float32 [T, C]: q, k, v after convolution and unit norm
+    at ``cols`` (q, k, v); ``proj``: output gate, beta and decay pre-activations at ``pcols`` (g, b, a)."""
+    _cuda_contig(qkv, A_log, dt_bias, norm_w, out)
+    _f32(qkv, A_log, dt_bias, norm_w)
+    _need(proj.stride(-1) == 1 and norm_w.numel() == dv and out.shape == (qkv.shape[0], H * dv), "gated_delta_scan: shapes")
+    _check(lib().nv_gated_delta_scan(_p(qkv), qkv.shape[1], cols["q"], cols["k"], cols["v"], G, _p(proj), dt(proj),
+                                     proj.stride(0), pcols["g"], pcols["b"], pcols["a"], _p(A_log), _p(dt_bias),
+                                     _p(batch.cu_rows), _p(batch.entry_slot), _p(S), _slot_stride(S), H, dk, dv, eps,
+                                     _p(norm_w), _p(out), dt(out), batch.S, _stream()), "gated_delta_scan")
+
+
+def qk_prepare_store(src, q0: int, k0: int, v0: int, positions, row_entry, block_table, q_weight, k_weight, eps: float,
+                     inv_freq, rot_dim: int, interleaved: bool, amplitude: float, q_out, k_cache, v_cache,
+                     Hq: int, Hkv: int, D: int, Dv: int, write_kv: bool, err: ErrorFlag) -> None:
+    """Per row: q and k heads RMS-normed over D (weights may be None), their first ``rot_dim`` elements turned in
+    pairs by the row's position, q to ``q_out`` [T, Hq * D], k and v to the row's place in their pages."""
+    _cuda_contig(positions, row_entry, block_table, q_weight, k_weight, inv_freq, q_out, k_cache, v_cache)
+    _i32(positions, row_entry, block_table)
+    _f32(q_weight, k_weight, inv_freq)
+    T = src.shape[0]
+    page = k_cache.shape[2]
+    _need(src.stride(-1) == 1 and q_out.shape == (T, Hq * D), "qk_prepare_store: shapes")
+    _need(k_cache.shape[1:] == (Hkv, page, D) and v_cache.shape[1:] == (Hkv, page, Dv) and k_cache.dtype == v_cache.dtype,
+          "qk_prepare_store: cache shapes")
+    _need(rot_dim == 0 or inv_freq.numel() >= rot_dim // 2, "qk_prepare_store: inv_freq")
+    _check(lib().nv_qk_prepare_store(_p(src), dt(src), src.stride(0), q0, k0, v0, _p(positions), _p(row_entry),
+                                     _p(block_table), block_table.shape[1], _p(q_weight), _p(k_weight), eps,
+                                     _p(inv_freq), rot_dim, (1 if interleaved else 0), amplitude, _p(q_out), dt(q_out),
+                                     _p(k_cache), _p(v_cache), dt(k_cache), Hq, Hkv, D, Dv, page,
+                                     (1 if write_kv else 0), _p(err.t), T, _stream()), "qk_prepare_store")
+
+
+def paged_attention_general(q, k_cache, v_cache, block_table, row_entry, positions, scale: float, window: int, out,
+                            Hq: int, Hkv: int, D: int, Dv: int, sink_score=None) -> None:
+    """Causal softmax attention of every row over its request's paged keys; values may be wider or narrower than
+    keys; ``sink_score``: a further key with that score and no value in every softmax (None: none)."""
+    _cuda_contig(q, k_cache, v_cache, block_table, row_entry, positions, out)
+    _i32(block_table, row_entry, positions)
+    T = q.shape[0]
+    _need(q.shape == (T, Hq * D) and out.shape == (T, Hq * Dv), "attention: shapes")
+    _check(lib().nv_paged_attention_general(_p(q), dt(q), _p(k_cache), _p(v_cache), dt(k_cache), _p(block_table),
+                                            block_table.shape[1], _p(row_entry), _p(positions), scale, window,
+                                            (0 if sink_score is None else 1), float(sink_score or 0.0), _p(out),
+                                            dt(out), T, Hq, Hkv, D, Dv, k_cache.shape[2], _stream()),
+           "paged_attention_general")
+
+
 # ----------------------------------------------------------------------------- fast products
 _num_sms = None
 

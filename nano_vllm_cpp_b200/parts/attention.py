@@ -20,48 +20,84 @@ class PagedAttention(Mixer):
     request read from the cache (so rows of this step see one another through it); ``out Wo^T``.
     Query head h reads kv head ``h // (Hq / Hkv)`` (src/hip_ops.hip:484).  ``scale`` defaults to
     ``1/sqrt(head_dim)`` (src/model.cpp:710).
+
+    Options beyond that, each off by default: values with a head size of their own (``v_head_dim``); an RMS norm
+    over every q and k head before the rotation, with one weight vector per side shared by the heads (``qk_norm_eps``);
+    a bias on the output projection (``out_bias``); a *sink* in every softmax, a key with the score ``sink_score``
+    and no value, so that ``p_j = exp(s_j) / (exp(sink_score) + sum_i exp(s_i))``; a position encoding that pairs
+    neighbouring elements or scales its cosines and sines.  ``names`` gives the tensors' names where they are not
+    the usual ones (keys: q, k, v, o, q_bias, k_bias, v_bias, o_bias, q_norm, k_norm).  A layer that uses one of
+    these options runs the general kernels (``ops.qk_prepare_store``, ``ops.paged_attention_general``).
     """
 
+    _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+              "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias",
+              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, bias: bool,
-                 position: PartSpec, window: int = 0, scale: float | None = None):
+                 position: PartSpec, window: int = 0, scale: float | None = None, v_head_dim: int | None = None,
+                 qk_norm_eps: float | None = None, out_bias: bool = False, sink_score: float | None = None,
+                 names: dict | None = None):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"head_dim {head_dim} is not supported: the attention kernels take multiples "
-                             "of 16 up to 256")
         self.hidden, self.Hq, self.Hkv, self.D = hidden_size, num_heads, num_kv_heads, head_dim
-        self.bias, self.window = bias, int(window)
+        self.Dv = int(v_head_dim) if v_head_dim else head_dim
+        self.bias, self.window, self.out_bias = bias, int(window), bool(out_bias)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.sink_score = None if sink_score is None else float(sink_score)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(float(head_dim))
         self.position = build_part("position", position) if isinstance(position, PartSpec) else position
+        self.names = dict(self._NAMES, **(names or {}))
+        self.general = (self.Dv != self.D or self.qk_norm_eps is not None or self.sink_score is not None
+                        or self.position.pairing != "halves" or self.position.amplitude != 1.0)
+        if self.general:
+            if head_dim < 1 or head_dim > 256 or self.Dv < 1 or self.Dv > 256:
+                raise ValueError(f"head sizes {head_dim} / {self.Dv} are not supported: the general attention kernels "
+                                 "take up to 256 elements per head")
+        elif head_dim % 16 or head_dim > 256:
+            raise ValueError(f"head_dim {head_dim} is not supported: the attention kernels take multiples "
+                             "of 16 up to 256")
 
     # ------------------------------------------------------------------ weights
     def tensor_specs(self, available=None):
-        H, q, kv = self.hidden, self.Hq * self.D, self.Hkv * self.D
-        s = {"q_proj.weight": TensorSpec((q, H)), "k_proj.weight": TensorSpec((kv, H)),
-             "v_proj.weight": TensorSpec((kv, H)), "o_proj.weight": TensorSpec((H, q))}
+        H, q, kv, vv, n = self.hidden, self.Hq * self.D, self.Hkv * self.D, self.Hkv * self.Dv, self.names
+        s = {n["q"]: TensorSpec((q, H)), n["k"]: TensorSpec((kv, H)),
+             n["v"]: TensorSpec((vv, H)), n["o"]: TensorSpec((H, self.Hq * self.Dv))}
         if self.bias:
-            s.update({"q_proj.bias": TensorSpec((q,), kind="vector"), "k_proj.bias": TensorSpec((kv,), kind="vector"),
-                      "v_proj.bias": TensorSpec((kv,), kind="vector")})
+            s.update({n["q_bias"]: TensorSpec((q,), kind="vector"), n["k_bias"]: TensorSpec((kv,), kind="vector"),
+                      n["v_bias"]: TensorSpec((vv,), kind="vector")})
+        if self.out_bias:
+            s[n["o_bias"]] = TensorSpec((H,), kind="vector")
+        if self.qk_norm_eps is not None:
+            s[n["q_norm"]] = TensorSpec((self.D,), init="ones", kind="vector")
+            s[n["k_norm"]] = TensorSpec((self.D,), init="ones", kind="vector")
         s.update(self.position.tensor_specs(available))      # a position encoding may have tensors of its own
         return s
 
     def load(self, fetch, ctx):
         self.ctx = ctx
+        n = self.names
         self.position.load(fetch, ctx)
         # q, k and v rows are stacked so that one product makes all three (src/model.cpp:508-513)
-        self.qkv_weight = _cat([fetch("q_proj.weight"), fetch("k_proj.weight"), fetch("v_proj.weight")])
+        self.qkv_weight = _cat([fetch(n["q"]), fetch(n["k"]), fetch(n["v"])])
         self.qkv_bias = None
         if self.bias:
-            self.qkv_bias = _cat([fetch("q_proj.bias"), fetch("k_proj.bias"), fetch("v_proj.bias")])
-        self.o_weight = fetch("o_proj.weight")
+            self.qkv_bias = _cat([fetch(n["q_bias"]), fetch(n["k_bias"]), fetch(n["v_bias"])])
+        self.o_weight = fetch(n["o"])
+        self.o_bias = fetch(n["o_bias"]) if self.out_bias else None
+        self.q_norm = self.k_norm = None
+        if self.qk_norm_eps is not None:
+            self.q_norm, self.k_norm = fetch(n["q_norm"]), fetch(n["k_norm"])
 
     def cache_spec(self):
-        return KVCacheSpec(self.Hkv, self.D, self.window)
+        return KVCacheSpec(self.Hkv, self.D, self.window, 0 if self.Dv == self.D else self.Dv)
 
     # ------------------------------------------------------------------ forward
     def forward(self, h, batch, cache):
         ctx = self.ctx
         T = h.shape[0]
+        if self.general:
+            return self._forward_general(h, batch, cache)
         qkv = linear(ctx, h, self.qkv_weight, ctx.act_dtype, bias=self.qkv_bias)
         bt = batch.block_tables[cache.group]
         ops.rope_store(qkv, batch.positions, self.position.inv_freq(), self.position.rotary_dim, cache.k, cache.v,
@@ -69,7 +105,25 @@ class PagedAttention(Mixer):
                        rot_positions=self.position.rotation_positions(batch), pair_axis=self.position.pair_axis())
         att = torch.empty((T, self.Hq * self.D), dtype=ctx.act_dtype, device=h.device)
         self._attend(qkv, cache, bt, batch, att)
-        return linear(ctx, att, self.o_weight, torch.float32)
+        return linear(ctx, att, self.o_weight, torch.float32, bias=self.o_bias)
+
+    def _forward_general(self, h, batch, cache):
+        """The projections come out in float32 (the head norms read them); q after norm and rotation, and the keys
+        and values in their pages, are in the activation dtype; scores, weights and sums are float32."""
+        ctx, T = self.ctx, h.shape[0]
+        Hq, Hkv, D, Dv = self.Hq, self.Hkv, self.D, self.Dv
+        proj = linear(ctx, h, self.qkv_weight, torch.float32, bias=self.qkv_bias)
+        bt = batch.block_tables[cache.group]
+        q = torch.empty((T, Hq * D), dtype=ctx.act_dtype, device=h.device)
+        pos = self.position
+        ops.qk_prepare_store(proj, 0, Hq * D, (Hq + Hkv) * D, batch.positions, batch.row_entry, bt, self.q_norm,
+                             self.k_norm, self.qk_norm_eps or 0.0, pos.inv_freq(), pos.rotary_dim,
+                             pos.pairing == "interleaved", pos.amplitude, q, cache.k, cache.v, Hq, Hkv, D, Dv,
+                             cache.write, ctx.err)
+        att = torch.empty((T, Hq * Dv), dtype=ctx.act_dtype, device=h.device)
+        ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale, self.window,
+                                    att, Hq, Hkv, D, Dv, sink_score=self.sink_score)
+        return linear(ctx, att, self.o_weight, torch.float32, bias=self.o_bias)
 
     def _attend(self, qkv, cache, bt, batch, att):
         """Which kernel runs which rows.  float32 runs keep the plain kernel for every row, so that their sums have

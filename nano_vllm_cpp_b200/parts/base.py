@@ -35,16 +35,22 @@ import torch
 @dataclass(frozen=True)
 class TensorSpec:
     shape: tuple
-    init: str = "normal"      # "normal": N(0, std) | "ones": 1 (+ N(0, norm_std) if asked) | "zeros"
+    init: str = "normal"      # "normal": N(0, std) | "ones": 1 (+ N(0, norm_std) if asked) | "zeros" | "near_zero": N(0, norm_std)
     kind: str = "matrix"      # "matrix" | "vector": vectors are held in float32 on the device
 
 
 @dataclass(frozen=True)
 class KVCacheSpec:
-    """Keys and values in pages; ``window`` > 0: only the last ``window`` positions are read."""
+    """Keys and values in pages; ``window`` > 0: only the last ``window`` positions are read.  ``v_head_dim`` > 0:
+    values have that many elements per head instead of ``head_dim``."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -53,6 +59,14 @@ class StateCacheSpec:
     the step that runs the request's first token."""
     shape: tuple
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class CompositeCacheSpec:
+    """What a mixer keeps when it keeps several things: pages and a state (two mixers side by side), or several
+    state arrays (a matrix, a vector and a scalar per head).  ``parts`` are cache specs, composites among them
+    allowed; the mixer's cache view then has one view per part, in the same order (``CacheView.parts``)."""
+    parts: tuple
 
 
 @dataclass
@@ -112,8 +126,17 @@ class RowMix:
         return (self.rows, self.index, self.weight, self.dense, self.gate_logit)
 
 
+@dataclass
+class StreamRows:
+    """What a layer hands on when nothing is left to add to the residual stream, but its rows already exist in the
+    activation dtype (the layer's last kernel wrote them): a next layer that reads the stream itself takes them."""
+    rows: torch.Tensor
+
+
 def resolve_branch(norm: Norm, branch):
     """What ``norm.forward`` may be given for ``branch``: the mix itself if the norm sums it, else its sum."""
+    if isinstance(branch, StreamRows):
+        return None
     if isinstance(branch, RowMix) and not norm.accepts_mix:
         return branch.sum()
     return branch
@@ -125,6 +148,8 @@ class PositionEncoding(Part):
     all turned by the row's place in its sequence, ``rotation_positions(batch)`` (int32 [T] or [T, axes]: the rows'
     coordinates) with ``pair_axis()`` (int32 [rotary_dim / 2]: which coordinate turns which pair)."""
     rotary_dim: int = 0
+    pairing: str = "halves"         # "halves": pairs (d, d + rotary_dim / 2); "interleaved": pairs (2d, 2d + 1)
+    amplitude: float = 1.0          # cosine and sine are multiplied by this
 
     def inv_freq(self):
         raise NotImplementedError
@@ -148,6 +173,14 @@ class FeedForward(Part):
     wants_f32_input: bool = False
 
     def forward(self, h, h32, batch):
+        raise NotImplementedError
+
+
+class TokenInput(Part):
+    """A branch that is computed from the residual stream's rows and from the rows' own token ids.
+    ``forward(h, batch)`` -> float32 ``[T, hidden]``."""
+
+    def forward(self, h, batch):
         raise NotImplementedError
 
 

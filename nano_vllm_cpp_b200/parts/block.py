@@ -14,7 +14,7 @@ feed-forward, a post-norm block) declares its own slots and is registered like a
 """
 from __future__ import annotations
 
-from .base import PartSpec, resolve_branch
+from .base import PartSpec, StreamRows, resolve_branch
 from .registry import register_part, build_part
 
 _DEFAULT_NAMES = {"norm1": "input_layernorm.", "mixer": "self_attn.", "norm2": "post_attention_layernorm.",
@@ -51,21 +51,22 @@ class Arrangement:
     residual stream, changed in place; ``pending`` is a branch output that has not been added to it yet (the sum
     is fused with whichever norm runs next), or None; ``cache`` is the layer call's ``CacheView``."""
     slots: dict = {}
+    optional: tuple = ()                # slots that a layer may leave out (their attribute is then None)
     cache_slot: str = "mixer"           # the slot whose part says what the layer keeps per request (None: nothing)
 
     def __init__(self, spec: LayerSpec):
         self.spec = spec
-        missing = [s for s in self.slots if s not in spec.parts]
+        missing = [s for s in self.slots if s not in spec.parts and s not in self.optional]
         extra = [s for s in spec.parts if s not in self.slots]
         if missing or extra:
             raise ValueError(f"arrangement {spec.arrangement!r} takes the parts {sorted(self.slots)}; "
                              f"missing {missing}, not taken {extra}")
         for slot, family in self.slots.items():
-            setattr(self, slot, build_part(family, spec.parts[slot]))
+            setattr(self, slot, build_part(family, spec.parts[slot]) if slot in spec.parts else None)
 
     def parts(self):
         """(tensor-name prefix inside the layer, part) for every part."""
-        return [(self.spec.prefix(slot), getattr(self, slot)) for slot in self.slots]
+        return [(self.spec.prefix(slot), getattr(self, slot)) for slot in self.slots if getattr(self, slot) is not None]
 
     def cache_spec(self):
         return getattr(self, self.cache_slot).cache_spec() if self.cache_slot else None
@@ -92,6 +93,44 @@ class PreNormBlock(Arrangement):
 
 
 register_part("arrangement", "prenorm", PreNormBlock)
+
+
+class BranchNormBlock(Arrangement):
+    """The norm on the sublayer's output only: ``x += norm1(mixer(x)); x += norm2(feed_forward(x))`` and, if the
+    layer has one, ``x += norm3(token_input(x))``.  The sublayers read the residual stream itself (its rows in the
+    activation dtype; each norm's kernel writes them after its sum).  A layer may have no feed-forward and no
+    token input.  Nothing is left pending: the stream is complete when the layer returns, and its rows are handed
+    on as ``StreamRows``."""
+    slots = {"norm1": "norm", "mixer": "mixer", "norm2": "norm", "feed_forward": "feed_forward",
+             "norm3": "norm", "token_input": "token_input"}
+    optional = ("norm2", "feed_forward", "norm3", "token_input")
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        if (self.norm2 is None) != (self.feed_forward is None) or (self.norm3 is None) != (self.token_input is None):
+            raise ValueError("a branch-norm layer's feed-forward and token input each come with their norm")
+
+    def forward(self, x, pending, batch, cache):
+        from .parallel import MixedBranches
+        if isinstance(pending, StreamRows):
+            h = pending.rows
+        elif pending is None:
+            h = self.norm1.add_normed(x, [])
+        else:
+            raise ValueError("a branch-norm layer takes the residual stream with nothing pending")
+        y = self.mixer.forward(h, batch, cache)
+        if isinstance(y, MixedBranches):
+            h = self.norm1.add_normed(x, y.branches, branch_weights=y.weights, mix_scale=y.scale)
+        else:
+            h = self.norm1.add_normed(x, [y])
+        if self.feed_forward is not None:
+            h = self.norm2.add_normed(x, [self.feed_forward.forward(h, h, batch)])
+        if self.token_input is not None:
+            h = self.norm3.add_normed(x, [self.token_input.forward(h, batch)])
+        return StreamRows(h)
+
+
+register_part("arrangement", "branch_norm", BranchNormBlock)
 
 
 def build_layer(spec: LayerSpec):

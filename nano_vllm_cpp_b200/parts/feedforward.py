@@ -41,6 +41,32 @@ class DenseSwiGLU(FeedForward):
         return linear(self.ctx, act, self.down, torch.float32)
 
 
+class DenseMLP(FeedForward):
+    """``down(act(up(h)))`` with ``act`` one of ``ops.ACTIVATIONS`` (gelu in its erf or tanh form, silu).  The
+    product's result is float32 and the activation is taken on that; its output is in the activation dtype."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "gelu_erf",
+                 up_name: str = "up_proj.weight", down_name: str = "down_proj.weight"):
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation must be one of {sorted(ops.ACTIVATIONS)}, found {activation!r}")
+        self.hidden, self.inter, self.activation = hidden_size, intermediate_size, activation
+        self.up_name, self.down_name = up_name, down_name
+
+    def tensor_specs(self, available=None):
+        return {self.up_name: TensorSpec((self.inter, self.hidden)), self.down_name: TensorSpec((self.hidden, self.inter))}
+
+    def load(self, fetch, ctx):
+        self.ctx = ctx
+        self.up, self.down = fetch(self.up_name), fetch(self.down_name)
+
+    def forward(self, h, h32, batch):
+        ctx = self.ctx
+        z = linear(ctx, h, self.up, torch.float32)
+        act = z if ctx.act_dtype == torch.float32 else torch.empty(z.shape, dtype=ctx.act_dtype, device=z.device)
+        ops.activation(z, act, self.activation)
+        return linear(ctx, act, self.down, torch.float32)
+
+
 class SparseMoeSwiGLU(FeedForward):
     """Per row (src/model.cpp:789-827; src/hip_ops.hip:813-893, 926-934):
 
@@ -279,4 +305,5 @@ def _cat(ts):
 
 
 register_part("feed_forward", "dense_swiglu", DenseSwiGLU)
+register_part("feed_forward", "dense_mlp", DenseMLP)
 register_part("feed_forward", "sparse_moe_swiglu", SparseMoeSwiGLU)

@@ -47,17 +47,29 @@ class ModelSpec:
         return list(self.order)
 
 
-class _Fetch:
-    """Fetches a part's tensors by local name from the model-wide source."""
+def _full_name(prefix: str, name: str) -> str:
+    """A part's tensor name as the model knows it: behind the part's prefix, or, if it starts with ``/``, a name
+    of the whole model (a tensor that several layers read)."""
+    return name[1:] if name.startswith("/") else prefix + name
 
-    def __init__(self, source, prefix):
-        self.source, self.prefix = source, prefix
+
+class _Fetch:
+    """Fetches a part's tensors by local name from the model-wide source.  A tensor of the whole model (``/name``)
+    is fetched once and handed to every part that asks for it."""
+
+    def __init__(self, source, prefix, shared: dict):
+        self.source, self.prefix, self.shared = source, prefix, shared
 
     def __call__(self, name):
-        return self.source.get(self.prefix + name)
+        full = _full_name(self.prefix, name)
+        if name.startswith("/"):
+            if full not in self.shared:
+                self.shared[full] = self.source.get(full)
+            return self.shared[full]
+        return self.source.get(full)
 
     def has(self, name):
-        return self.source.has(self.prefix + name)
+        return self.source.has(_full_name(self.prefix, name))
 
 
 class Model:
@@ -89,9 +101,12 @@ class Model:
         s = self.spec
         out = {s.embed_name: TensorSpec((s.vocab_size, s.hidden_size))}
         for prefix, part in self._named_parts():
-            part_has = (lambda n, p=prefix: has(p + n)) if has is not None else None
+            part_has = (lambda n, p=prefix: has(_full_name(p, n))) if has is not None else None
             for name, ts in part.tensor_specs(part_has).items():
-                out[prefix + name] = ts
+                full = _full_name(prefix, name)
+                if full in out and tuple(out[full].shape) != tuple(ts.shape):
+                    raise ValueError(f"tensor {full!r} is wanted with the shapes {out[full].shape} and {ts.shape}")
+                out[full] = ts
         if not s.tie_word_embeddings:
             out[s.lm_head_name] = TensorSpec((s.vocab_size, s.hidden_size))
         return out
@@ -111,8 +126,9 @@ class Model:
         self.ctx = ctx
         s = self.spec
         self.embed = source.get(s.embed_name)
+        shared: dict = {}
         for prefix, part in self._named_parts():
-            part.load(_Fetch(source, prefix), ctx)
+            part.load(_Fetch(source, prefix, shared), ctx)
         self.lm_head = self.embed if s.tie_word_embeddings else source.get(s.lm_head_name)
 
     # ------------------------------------------------------------------ forward

@@ -16,15 +16,34 @@ class RMSNorm(Norm):
     """
     accepts_mix = True
 
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, weight_offset: float = 0.0, weight_name: str = "weight"):
+        """``weight_offset``: the stored weight lies around zero and the multiplier is ``weight_offset`` + weight
+        (1.0 for the "one plus weight" form); the sum is taken once, in float32, when the weight is loaded.
+        ``weight_name``: the tensor's name behind the part's prefix."""
         self.size, self.eps = size, float(eps)
+        self.weight_offset, self.weight_name = float(weight_offset), weight_name
 
     def tensor_specs(self, available=None):
-        return {"weight": TensorSpec((self.size,), init="ones", kind="vector")}
+        return {self.weight_name: TensorSpec((self.size,), init="near_zero" if self.weight_offset else "ones", kind="vector")}
 
     def load(self, fetch, ctx):
         self.ctx = ctx
-        self.weight = fetch("weight")
+        self.weight = fetch(self.weight_name)
+        if self.weight_offset:
+            self.weight = (self.weight.float() + self.weight_offset).contiguous()
+
+    def add_normed(self, x, branches, want_rows: bool = True, *, branch_weights=None, mix_scale: float = 1.0):
+        """``x += rms(y) * w`` in place, the norm on the branch and not on the stream: ``y`` is the one branch, or
+        ``mix_scale`` times the sum of the branches each RMS-normed (this norm's eps) with its own weight.  Returns the
+        stream's rows after the sum in the run's activation dtype (the stream itself in a float32 run), which the
+        next sublayer's products read; None if not wanted.  No branches: only the rows are made."""
+        out = None
+        if want_rows:
+            out = x if self.ctx.act_dtype == torch.float32 else torch.empty(x.shape, dtype=self.ctx.act_dtype, device=x.device)
+        if branches or (out is not None and out is not x):
+            ops.branch_norm_add(x, branches, self.weight, self.eps, None if out is x else out,
+                                branch_weights=branch_weights, mix_scale=mix_scale)
+        return out
 
     def forward(self, x, branch, want_f32=False):
         out = torch.empty(x.shape, dtype=self.ctx.act_dtype, device=x.device)

@@ -8,13 +8,14 @@ POSITION_ENCODINGS: dict = {}
 MIXERS: dict = {}
 FEED_FORWARDS: dict = {}
 ARRANGEMENTS: dict = {}
+TOKEN_INPUTS: dict = {}
 
 _TABLES = {"norm": NORMS, "position": POSITION_ENCODINGS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS,
-           "arrangement": ARRANGEMENTS}
+           "arrangement": ARRANGEMENTS, "token_input": TOKEN_INPUTS}
 
 
 def register_part(family: str, kind: str, cls) -> None:
-    """``family``: norm, position, mixer, feed_forward or arrangement."""
+    """``family``: norm, position, mixer, feed_forward, token_input or arrangement."""
     _TABLES[family][kind] = cls
 
 

@@ -108,8 +108,10 @@ class RandomSource:
 
     def stored(self, name: str) -> torch.Tensor:
         spec = self.specs[name]
-        if spec.init == "zeros":
+        if spec.init == "zeros" or (spec.init == "near_zero" and not self.norm_std > 0):
             return torch.zeros(spec.shape, dtype=self.store_dtype, device=self.device)
+        if spec.init == "near_zero":
+            return self._draw(name, spec.shape, 0.0, self.norm_std)
         if spec.init == "ones":
             if self.norm_std > 0:
                 return self._draw(name, spec.shape, 1.0, self.norm_std)
@@ -125,9 +127,9 @@ def write_model_folder(config: dict, out_dir: str, seed: int, *, std: float | No
                        norm_std: float = 0.0, dtype: str = "bfloat16") -> str:
     """Random-weights mode: writes ``config.json`` and ``model.safetensors`` for the architecture
     that ``config`` names, drawn from ``seed``.  Returns ``out_dir``."""
-    from ..config.registry import get_architecture
+    from ..config.registry import get_architecture, architecture_name
     from ..parts import Model
-    arch = get_architecture(config["architectures"][0])
+    arch = get_architecture(architecture_name(config))
     cfg = arch.config_from_dict(config)
     spec = arch.build_model(cfg)
     model = Model(spec)
