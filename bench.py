@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --design bizodra [--design-sizes s,m]     (another measurement, see ``design_bench``)
 
 Default run: the layer sizes of the Qwen1.5-MoE-A2.7B shape with random bfloat16 weights, a batch
 of 8 sequences each at a 2,048-token context; a step is one decode step of that batch.  ``value``
@@ -198,6 +199,173 @@ def kernel_times(runner, cfg, args, P, fill_context, StepEntry, ops, torch, g, V
         runner.cuda_graphs = graphs
     return out
 
+# ---------------------------------------------------------------------------------------------------------------
+# --design bizodra: prefill and decode throughput of the Bizodra decoder at layer sizes that resemble a real model's
+# (random weights), beside the closest existing model at equal size: a dense Qwen2 decoder (no experts) with the same
+# width, depth, heads, head size and vocabulary and an MLP of the same parameter count.  One JSON line.
+DESIGN_SIZES = {
+    "s": dict(width=1024, layers=4, heads=8, kv_heads=2, dim=128, ff=4096, vocab=32000),
+    "m": dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, ff=8192, vocab=32000),
+}
+
+
+def bizodra_config(z):
+    W, H, G, D = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    lstm = {"heads": H, "dim": D, "vdim": D, "gate_cap": 15.0}
+    par = {"left": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5,
+                    "rot": {"dims": D, "base": 1e6, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+           "right": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "conv": 4}}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    kinds = [("mlstm", lstm), ("parallel", par), ("mlstm_2", lstm), ("parallel", par)]
+    return {"architecture": "Bizodra", "vocab": z["vocab"], "width": W, "norm": {"eps": 1e-6}, "token_side": {"dim": 64},
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(z["layers"])]}
+
+
+def dense_qwen_config(z):
+    return dict(architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe", num_hidden_layers=z["layers"],
+                hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+                head_dim=z["dim"], num_experts=0, intermediate_size=(2 * z["ff"] // 3 + 127) // 128 * 128,
+                vocab_size=z["vocab"], rope_theta=1e6, rms_norm_eps=1e-6, max_position_embeddings=32768,
+                tie_word_embeddings=False, qkv_bias=True)
+
+
+def design_bench(args) -> int:
+    import torch
+    from nano_vllm_cpp_b200.csrc import ops
+    from nano_vllm_cpp_b200.engine.batch import StepEntry
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    P, peak_src = peaks()
+    T, ctx_len, batches = args.prefill_tokens, args.context, [1, args.batch, 64]
+    rows = []
+    clocks = ClockSampler()
+    clocks.start()
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps):
+        ts = []
+        for _ in range(reps):
+            torch.cuda.synchronize()
+            a, b = ev(), ev()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+
+    for size in args.design_sizes.split(","):
+        z = DESIGN_SIZES[size]
+        for model, cfg in (("bizodra", bizodra_config(z)), ("qwen2_dense", dense_qwen_config(z))):
+            work = tempfile.mkdtemp(prefix="bench_design_")
+            with open(os.path.join(work, "config.json"), "w") as f:
+                json.dump(cfg, f)
+            need = 64 * (ctx_len + args.steps + args.warmup + 32) + T + 64
+            runner = ModelRunner(work, dtype="bfloat16", num_pages=(need + 15) // 16, max_requests=65,
+                                 max_model_len=max(T, ctx_len + args.steps + args.warmup + 32) + 16, random_seed=SEED,
+                                 std=0.02, norm_std=0.02)
+            g = torch.Generator().manual_seed(SEED)
+            V = z["vocab"]
+            params = sum(t.numel() for t in _model_tensors(runner.model))
+            ids = torch.randint(0, V, (T,), generator=g).tolist()
+
+            def prefill():
+                runner.step([StepEntry("pf", ids, [T - 1])], check=False)
+                runner.close("pf")
+            for _ in range(args.warmup):
+                prefill()
+            ms = timed(prefill, 3)
+            row = {"size": size, "model": model, "params_m": round(params / 1e6, 1),
+                   "prefill": {"tokens": T, "ms": round(ms, 3), "tokens_per_s": round(T / ms * 1e3, 1)}, "decode": []}
+            # the prompt's kernels one by one (outside graphs, an event between any two)
+            graphs, runner.cuda_graphs = runner.cuda_graphs, False
+            with ops.KernelTimes() as kt:
+                runner.step([StepEntry("kt", ids, [T - 1])], check=False)
+            runner.close("kt")
+            row["prefill_kernels"] = [{"name": r["name"], "calls": r["calls"], "ms": round(r["ms"], 3),
+                                       **({"frac_bf16": round(r["flops"] / (r["ms"] * 1e-3) / (P["bf16_tflops"] * 1e12), 3)} if r["flops"] else {})}
+                                      for r in kt.summary()[:8]]
+            runner.cuda_graphs = graphs
+            for B in batches:
+                rids = [f"d{B}_{i}" for i in range(B)]
+                for rid in rids:
+                    runner.open(rid)
+                    runner.manager.extend(rid, 0, ctx_len)
+                    runner.manager.commit(rid, ctx_len)
+                _fill_caches(runner.cache.views, torch)
+                toks = torch.randint(0, V, (B,), generator=g).tolist()
+                entries = [StepEntry(r, [t], [0]) for r, t in zip(rids, toks)]
+                temps, us = [0.0] * B, [0.5] * B
+                for _ in range(args.warmup):
+                    runner.step_tokens(entries, temps, us)
+                torch.cuda.synchronize()
+                a, b = ev(), ev()
+                a.record()
+                for _ in range(args.steps):
+                    runner.collect(runner.launch_tokens(entries, temps, us))
+                b.record()
+                torch.cuda.synchronize()
+                ms = a.elapsed_time(b) / args.steps
+                row["decode"].append({"batch": B, "context": ctx_len, "ms_per_step": round(ms, 4),
+                                      "tokens_per_s": round(B / ms * 1e3, 1),
+                                      "frac_hbm_weights": round(2 * params / (ms * 1e-3) / (P["hbm_gbs"] * 1e9), 3)})
+                if B == args.batch:
+                    graphs, runner.cuda_graphs = runner.cuda_graphs, False
+                    runner.step(entries, check=False)
+                    with ops.KernelTimes() as kt:
+                        for _ in range(4):
+                            ops.delay(20000)
+                            runner.step(entries, check=False)
+                    row["decode_kernels"] = [{"name": r["name"], "calls": r["calls"] // 4, "ms": round(r["ms"] / 4, 4)}
+                                             for r in kt.summary()[:8]]
+                    runner.cuda_graphs = graphs
+                for rid in rids:
+                    runner.close(rid)
+            runner.ctx.err.check("design bench")
+            rows.append(row)
+            del runner
+            torch.cuda.empty_cache()
+    print(json.dumps({"metric": "design_throughput", "design": "bizodra", "beside": "qwen2_dense", "dtype": "bf16",
+                      "data": "synthetic", "peaks": {"source": peak_src, **P}, "steps": args.steps, "warmup": args.warmup,
+                      "clocks": clocks.stop(), "rows": rows}))
+    return 0
+
+
+def _model_tensors(model):
+    seen, out = set(), []
+
+    def walk(o, depth=0):
+        import torch
+        if isinstance(o, torch.Tensor):
+            if o.data_ptr() not in seen and o.is_floating_point():
+                seen.add(o.data_ptr())
+                out.append(o)
+        elif isinstance(o, (list, tuple)):
+            for x in o:
+                walk(x, depth)
+        elif hasattr(o, "__dict__") and depth < 6 and type(o).__module__.startswith("nano_vllm_cpp_b200.parts"):
+            for k, x in vars(o).items():
+                if k not in ("ctx", "spec"):
+                    walk(x, depth + 1)
+    walk(model.layers)
+    walk(model.final_norm)
+    walk([model.embed, model.lm_head])
+    return out
+
+
+def _fill_caches(views, torch):
+    for v in views:
+        if v is None:
+            continue
+        if v.kind == "multi":
+            _fill_caches(v.parts, torch)
+        elif v.kind == "kv" and v.write:
+            v.k.normal_(0, 0.5)
+            v.v.normal_(0, 0.5)
+        elif v.kind == "state" and v.write:
+            v.state.normal_(0, 0.05)
+
 
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -214,6 +382,9 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-kernel-times", action="store_true", help="skip the per-kernel-class CUDA-event times")
+    ap.add_argument("--design", default=None, choices=["bizodra"],
+                    help="instead of the default workload: this design beside the closest existing model at equal size")
+    ap.add_argument("--design-sizes", default="s,m", help="which of the sizes of --design to run, with commas")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -226,6 +397,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design:
+        return design_bench(args)
 
     import torch
     from nano_vllm_cpp_b200.csrc import ops

@@ -65,6 +65,8 @@ struct DecArgs {
   int* err;
   float scale;
   int q_dt, out_dt, q_stride, max_blocks, window, Hq, Hkv, D, page, splits, stages;
+  int has_sink;           // the softmax's denominator also holds exp(sink): a key with that score and no value
+  float sink;             // (the lane-per-chunk kernel and the merges add it; the tensor-core form does not know it)
 };
 
 // Called by every thread of a block once the block has written its split's partial results for the query heads
@@ -96,6 +98,7 @@ __device__ __forceinline__ void merge_when_last(const DecArgs& a, int r, int t, 
       ll = fmaf(__ldcg(a.part_ml + (pi + s) * 2 + 1), sc, ll);
       o = fmaf(__ldcg(a.part_o + (pi + s) * D + d), sc, o);
     }
+    if (a.has_sink) ll += __expf(a.sink - mm);
     st_dt(a.out, a.out_dt, ((size_t)t * a.Hq + h) * D + d, o * (ll > 0.f ? 1.f / ll : 0.f));
   }
 }
@@ -303,6 +306,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) attention_decode_kernel(DecA
     }
     const int h = kvh * G + g0 + g;
     if (a.splits == 1) {
+      if (a.has_sink) ll += __expf(a.sink - mm);
       st_dt(a.out, a.out_dt, ((size_t)t * a.Hq + h) * D + d, ll > 0.f ? o / ll : 0.f);
     } else {
       const size_t pi = ((size_t)r * a.Hq + h) * a.splits + split;
@@ -601,7 +605,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
 // Combines the splits of one (row, head) in split order.
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int* __restrict__ rows, void* __restrict__ out, int out_dt,
-                                              int Hq, int D, int splits) {
+                                              int Hq, int D, int splits, int has_sink, float sink) {
   const int r = blockIdx.x, h = blockIdx.y;
   const int t = rows ? rows[r] : r;
   const size_t pi = ((size_t)r * Hq + h) * splits;
@@ -611,6 +615,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(pi + s) * 2]);
   float ll = 0.f;
   for (int s = 0; s < splits; ++s) ll = fmaf(part_ml[(pi + s) * 2 + 1], __expf(part_ml[(pi + s) * 2] - mm), ll);
+  if (has_sink) ll += __expf(sink - mm);
   const float inv = ll > 0.f ? 1.f / ll : 0.f;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float o = 0.f;
@@ -717,7 +722,11 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
                                const int* block_table, int max_blocks, const int* row_entry, const int* positions,
                                const int* rows, int R, float scale, int window, void* out, int out_dt, int Hq,
                                int Hkv, int D, int page, int num_pages, int splits, float* scratch, int* err,
-                               int* split_count, int split_count_len, cudaStream_t stream) {
+                               int* split_count, int split_count_len, int has_sink, float sink_score,
+                               int float_weights, cudaStream_t stream) {
+  // has_sink: a further key with the score sink_score and no value in every softmax.  float_weights: the weights
+  // stay float32 in their product with the values (the lane-per-chunk kernel; the tensor-core form rounds them to
+  // bfloat16).  Either one keeps the tensor-core form out.
   if (!dt_ok(q_dt) || !dt_ok(cache_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
   if (D <= 0 || D > 256 || D % 8 || Hkv <= 0 || Hq % Hkv || page % 16) return NV_ERR_UNSUPPORTED;
   const int esize = cache_dt == NV_DT_BF16 ? 2 : 4;
@@ -734,6 +743,7 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   a.part_o = scratch;
   a.part_ml = scratch ? scratch + (size_t)R * Hq * splits * D : nullptr;
   a.err = err;
+  a.has_sink = has_sink; a.sink = sink_score;
   // `split_count`: zeros (R * Hq of them are enough), kept zero from launch to launch by the kernel: the splits are
   // then added up by the block that finishes last instead of by a second kernel.  For a few rows only: with many,
   // the last blocks' sums lengthen the kernel's tail by more than the second kernel's launch costs (measured per
@@ -749,7 +759,8 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   // next page is on its way while it works on one (with one stage per warp a warp sat out the whole memory latency
   // between two pages), and three CTAs of 76 KB still share a multiprocessor.  Deeper rings lose CTAs and time.
   int tc_stages = stages / WARPS * WARPS;
-  if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS) {
+  if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS && !has_sink &&
+      !float_weights) {
     a.stages = tc_stages;
     // tensor-core form (a page of keys per warp); its blocks take up to 16 query heads of a kv head
     rc = D == 64 ? launch_decode_tc<64>(a, R, kc, vc, num_pages, scale, stream)
@@ -769,7 +780,7 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   if (splits > 1 && !a.split_count) {
     dim3 grid(R, Hq);
     NV_RETURN_IF(launch_dep(attention_decode_merge_kernel, grid, dim3(128), 0, stream, (const float*)a.part_o,
-                            (const float*)a.part_ml, rows, out, out_dt, Hq, D, splits));
+                            (const float*)a.part_ml, rows, out, out_dt, Hq, D, splits, has_sink, sink_score));
   }
   NV_RETURN_LAST();
 }
@@ -827,7 +838,7 @@ NV_API int nv_attention_decode_noalloc(const void* qkv, int q_dt, int q_stride, 
   }
   return nv_attention_decode(qkv, q_dt, q_stride, kc, vc, cache_dt, block_table, max_blocks, row_entry, positions,
                              rows, R, scale, window, out, out_dt, Hq, Hkv, D, page, num_pages, splits,
-                             g_noalloc_ptr[dev], g_noalloc_err_ptr[dev], nullptr, 0, stream);
+                             g_noalloc_ptr[dev], g_noalloc_err_ptr[dev], nullptr, 0, 0, 0.f, 0, stream);
 }
 
 NV_API int nv_attention_decode_noalloc_status(void) {

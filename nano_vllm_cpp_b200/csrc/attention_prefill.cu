@@ -6,6 +6,10 @@
 // each of its 8 warps owns 16 rows.  Keys and values are gathered page by page into shared memory in
 // tiles of 64 keys with cp.async (double-buffered), S = Q K^T and O += P V run as m16n8k16 bf16
 // MMAs with float32 accumulators, and the softmax is the online form in float32 registers.
+// The weights P are float32; for the product with V they are rounded to bfloat16 (terms = 1) or split into a sum
+// of two or three bfloat16 numbers, each term a product of its own into the same accumulators, so that with three
+// terms a weight enters with all the bits of the float.  A sink (a further key with a fixed score and no value)
+// is added to the softmax's denominator at the end.
 // Row at position p sees keys [max(0, p + 1 - window), p]; the mask is applied per element, so
 // a tile may mix rows with different ranges.  The rows of this step are already in the cache when
 // the kernel runs, so a portion sees its own earlier rows there.
@@ -30,6 +34,9 @@ struct PfArgs {
   float scale_log2;         // scale * log2(e)
   int S, q_stride, max_blocks, window, Hq, Hkv, D, page;
   int min_rows;             // entries with fewer rows are left to another kernel
+  int has_sink;             // the softmax's denominator also holds exp(sink): a key with that score and no value
+  float sink_log2;          // the sink's score times log2(e)
+  int terms;                // the weights enter P V as one bfloat16 term (rounded) or three (all 24 bits of the float)
 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -61,7 +68,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // DP: head dimension rounded up to 32, 64, 128 or 256 (sizes the shared memory and the accumulators).
-template <int DP, int BM>
+// TERMS: how many bfloat16 terms a weight is split into (1 or 3).
+template <int DP, int BM, int TERMS>
 __global__ void __launch_bounds__(BM * 2, DP <= 128 ? 2 : 1) attention_prefill_kernel(PfArgs a) {
   constexpr int PF_THREADS = BM * 2;
   constexpr int LDS = DP + 8;                      // row stride (elements): 16 bytes of padding against bank conflicts
@@ -235,11 +243,24 @@ __global__ void __launch_bounds__(BM * 2, DP <= 128 ? 2 : 1) attention_prefill_k
     // ---- O += P V
 #pragma unroll
     for (int kb16 = 0; kb16 < BN / 16; ++kb16) {
-      uint32_t pa[4];
-      pa[0] = pack_bf16(s[2 * kb16][0], s[2 * kb16][1]);
-      pa[1] = pack_bf16(s[2 * kb16][2], s[2 * kb16][3]);
-      pa[2] = pack_bf16(s[2 * kb16 + 1][0], s[2 * kb16 + 1][1]);
-      pa[3] = pack_bf16(s[2 * kb16 + 1][2], s[2 * kb16 + 1][3]);
+      uint32_t pt[TERMS][4];
+      {
+        float w[8] = {s[2 * kb16][0], s[2 * kb16][1], s[2 * kb16][2], s[2 * kb16][3],
+                      s[2 * kb16 + 1][0], s[2 * kb16 + 1][1], s[2 * kb16 + 1][2], s[2 * kb16 + 1][3]};
+#pragma unroll
+        for (int term = 0; term < TERMS; ++term) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const uint32_t pk = pack_bf16(w[2 * u], w[2 * u + 1]);
+            pt[term][u] = pk;
+            if (term + 1 < TERMS) {
+              w[2 * u] -= __uint_as_float(pk << 16);             // what the rounding left: the next term
+              w[2 * u + 1] -= __uint_as_float(pk & 0xffff0000u);
+            }
+          }
+        }
+      }
+      const uint32_t* pa = pt[0];
 #pragma unroll
       for (int d4 = 0; d4 < DP / 64; ++d4) {
         if (d4 * 64 < D) {
@@ -257,6 +278,11 @@ __global__ void __launch_bounds__(BM * 2, DP <= 128 ? 2 : 1) attention_prefill_k
             if (dp * 16 < D) {
               mma16816(o[2 * dp], pa, vf[u][0], vf[u][1]);
               mma16816(o[2 * dp + 1], pa, vf[u][2], vf[u][3]);
+#pragma unroll
+              for (int term = 1; term < TERMS; ++term) {
+                mma16816(o[2 * dp], pt[term], vf[u][0], vf[u][1]);
+                mma16816(o[2 * dp + 1], pt[term], vf[u][2], vf[u][3]);
+              }
             }
           }
         }
@@ -270,6 +296,11 @@ __global__ void __launch_bounds__(BM * 2, DP <= 128 ? 2 : 1) attention_prefill_k
                     b2, b3);
             mma16816(o[2 * dp], pa, b0, b1);
             mma16816(o[2 * dp + 1], pa, b2, b3);
+#pragma unroll
+            for (int term = 1; term < TERMS; ++term) {
+              mma16816(o[2 * dp], pt[term], b0, b1);
+              mma16816(o[2 * dp + 1], pt[term], b2, b3);
+            }
           }
         }
       }
@@ -283,6 +314,10 @@ __global__ void __launch_bounds__(BM * 2, DP <= 128 ? 2 : 1) attention_prefill_k
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  if (a.has_sink) {                                 // relative to the same reference as the sums: exp2(sink - m)
+    l_lo += exp2f(a.sink_log2 - (m_lo == -INFINITY ? 0.f : m_lo * a.scale_log2));
+    l_hi += exp2f(a.sink_log2 - (m_hi == -INFINITY ? 0.f : m_hi * a.scale_log2));
+  }
   const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
 #pragma unroll
   for (int i = 0; i < DP / 8; ++i) {
@@ -296,18 +331,18 @@ __global__ void __launch_bounds__(BM * 2, DP <= 128 ? 2 : 1) attention_prefill_k
   }
 }
 
-template <int DP, int BM>
+template <int DP, int BM, int TERMS>
 int launch_prefill_bm(const PfArgs& a, int max_tiles, cudaStream_t s) {
   const size_t smem = (size_t)(BM + 4 * BN) * (DP + 8) * sizeof(bf16);
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP, BM, TERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
   dim3 grid(max_tiles, a.Hq);
-  attention_prefill_kernel<DP, BM><<<grid, BM * 2, smem, s>>>(a);
+  attention_prefill_kernel<DP, BM, TERMS><<<grid, BM * 2, smem, s>>>(a);
   NV_RETURN_LAST();
 }
 
@@ -317,7 +352,8 @@ int launch_prefill_bm(const PfArgs& a, int max_tiles, cudaStream_t s) {
 template <int DP>
 int launch_prefill(const PfArgs& a, int max_tiles64, int num_sms, cudaStream_t s) {
   (void)num_sms;
-  return launch_prefill_bm<DP, 128>(a, max_tiles64, s);
+  if (a.terms == 3) return launch_prefill_bm<DP, 128, 3>(a, max_tiles64, s);
+  return launch_prefill_bm<DP, 128, 1>(a, max_tiles64, s);
 }
 
 }  // namespace
@@ -331,8 +367,9 @@ NV_API int nv_attention_prefill_tile_rows() { return 64; }
 NV_API int nv_attention_prefill(const void* qkv, int q_stride, const void* kc, const void* vc,
                                 const int* block_table, int max_blocks, const int* cu_rows, const int* entry_pos0,
                                 int S, int max_tiles, float scale, int window, void* out, int Hq, int Hkv, int D,
-                                int page, int min_rows, cudaStream_t stream) {
-  if (D <= 0 || D > 256 || D % 16 || Hkv <= 0 || Hq % Hkv) return NV_ERR_UNSUPPORTED;
+                                int page, int min_rows, int has_sink, float sink_score, int terms,
+                                cudaStream_t stream) {
+  if (D <= 0 || D > 256 || D % 16 || Hkv <= 0 || Hq % Hkv || (terms != 1 && terms != 3)) return NV_ERR_UNSUPPORTED;
   if (q_stride % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15)) return NV_ERR_UNSUPPORTED;
   if (S == 0 || max_tiles == 0) return NV_OK;
   PfArgs a;
@@ -342,6 +379,7 @@ NV_API int nv_attention_prefill(const void* qkv, int q_stride, const void* kc, c
   a.S = S; a.q_stride = q_stride; a.max_blocks = max_blocks; a.window = window; a.Hq = Hq; a.Hkv = Hkv; a.D = D;
   a.page = page;
   a.min_rows = min_rows;
+  a.has_sink = has_sink; a.sink_log2 = sink_score * 1.4426950408889634f; a.terms = terms;
   static int num_sms = 0;
   if (!num_sms) {
     int dev = 0;

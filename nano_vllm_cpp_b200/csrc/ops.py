@@ -361,8 +361,12 @@ def attention_decode_usable(k_cache, D: int) -> bool:
 
 
 def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, scale: float, window: int, out,
-                     Hq: int, Hkv: int, D: int, max_context: int, rows=None, err=None) -> None:
-    """One query row per request (``rows``: which batch rows; None = all) against its paged keys."""
+                     Hq: int, Hkv: int, D: int, max_context: int, rows=None, err=None, sink_score=None,
+                     float_weights: bool = False) -> None:
+    """One query row per request (``rows``: which batch rows; None = all) against its paged keys.  ``qkv``: rows
+    whose first Hq * D elements are the query heads.  ``sink_score``: a further key with that score and no value
+    in every softmax.  ``float_weights``: the weights stay float32 in the product with the values (the kernel
+    that gives a lane a chunk of a key; the tensor-core form rounds them to bfloat16)."""
     _cuda_contig(qkv, k_cache, v_cache, block_table, row_entry, positions, out, rows)
     _i32(block_table, row_entry, positions, rows)
     R = qkv.shape[0] if rows is None else rows.numel()
@@ -378,7 +382,9 @@ def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, s
                                  _p(positions), _p(rows), R, scale, window, _p(out),
                                  dt(out), Hq, Hkv, D, page, k_cache.shape[0],
                                  splits, _p(scratch), _p(err.t if err is not None else _global_err().t),
-                                 _p(counts), (counts.numel() if counts is not None else 0), _stream()),
+                                 _p(counts), (counts.numel() if counts is not None else 0),
+                                 (0 if sink_score is None else 1), float(sink_score or 0.0),
+                                 (1 if float_weights else 0), _stream()),
            "attention_decode")
 
 
@@ -400,10 +406,13 @@ def attention_prefill_tile_rows() -> int:
 
 def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, max_tiles: int, scale: float,
                       window: int, out, Hq: int, Hkv: int, D: int, err=None, min_rows: int = 1,
-                      kernel: str = "auto") -> None:
+                      kernel: str = "auto", sink_score=None, weight_terms: int = 1) -> None:
     """bfloat16 rows of any mix of portions against their paged keys: the tcgen05 kernel for head sizes 64 and
     128 and pages of 16, 32 or 64 keys, else the mma.sync kernel (``kernel="mma"`` asks for that one).  Entries
-    with fewer than ``min_rows`` rows are skipped and their rows of ``out`` left as they are."""
+    with fewer than ``min_rows`` rows are skipped and their rows of ``out`` left as they are.
+    ``sink_score`` (a further key with that score and no value in every softmax) and ``weight_terms`` = 3 (the
+    float32 weights enter the product with the values as three bfloat16 terms, all their bits) are the mma.sync
+    kernel's."""
     _cuda_contig(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, out)
     _i32(block_table, cu_rows, entry_pos0)
     _need(qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
@@ -413,6 +422,8 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, m
     L = lib()
     page = k_cache.shape[2]
     _need(kernel in ("auto", "mma"), "attention_prefill: kernel is 'auto' or 'mma'")
+    if sink_score is not None or weight_terms != 1:
+        kernel = "mma"
     if kernel == "auto" and L.nv_attention_prefill_tc_usable(D, page):
         _check(L.nv_attention_prefill_tc(_p(qkv), qkv.shape[1], qkv.shape[0], _p(k_cache), _p(v_cache),
                                          k_cache.shape[0], _p(block_table), block_table.shape[1],
@@ -425,7 +436,8 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, m
     _check(L.nv_attention_prefill(_p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table),
                                   block_table.shape[1], _p(cu_rows), _p(entry_pos0), S,
                                   max_tiles, scale, window, _p(out), Hq, Hkv,
-                                  D, page, min_rows, _stream()), "attention_prefill")
+                                  D, page, min_rows, (0 if sink_score is None else 1), float(sink_score or 0.0),
+                                  weight_terms, _stream()), "attention_prefill")
 
 
 def gemm_plain_tile_m() -> int:
@@ -782,14 +794,30 @@ def scan_usable(dk: int, dv: int, parts: int = 1) -> bool:
     return bool(lib().nv_scan_usable(dk, dv, parts))
 
 
+def col_scan_usable(dk: int, dv: int) -> bool:
+    """Whether the scans that keep a column of a head's matrix in a thread's registers take these sizes."""
+    return bool(lib().nv_col_scan_usable(dk, dv))
+
+
 def mlstm_scan(proj, cols: dict, batch, S, n, m, H: int, dk: int, dv: int, cap: float, eps: float, norm_w, out,
-               *, den_eps: float = 1e-6) -> None:
+               *, den_eps: float = 1e-6, columns: bool = True) -> None:
     """The matrix memory with exponential gating, row by row per entry, from and to the entries' states.
     ``proj`` float32 [T, P] holds q, k, v, the output gate and the two gate pre-activations at ``cols``
-    (keys q, k, v, g, i, f)."""
+    (keys q, k, v, g, i, f).  ``columns``: the kernel that keeps a column per thread where it takes the sizes
+    (keys up to 128 long), else the one that keeps the matrix in shared memory."""
     _cuda_contig(proj, norm_w, out)
     _f32(proj, norm_w)
     _need(norm_w.numel() in (dv, H * dv) and out.shape == (proj.shape[0], H * dv), "mlstm_scan: shapes")
+    if columns and col_scan_usable(dk, dv):
+        T = proj.shape[0]
+        raw = torch.empty((T, H, dv + 2), dtype=torch.float32, device=proj.device)
+        gate_buf = torch.empty((T, H, 2), dtype=torch.float32, device=proj.device)
+        _check(lib().nv_mlstm_col_scan(_p(proj), proj.stride(0), cols["q"], cols["k"], cols["v"], cols["g"], cols["i"],
+                                       cols["f"], _p(batch.cu_rows), _p(batch.entry_slot), _p(S), _slot_stride(S), _p(n),
+                                       _slot_stride(n), _p(m), _slot_stride(m), H, dk, dv, cap, float(dk) ** -0.5,
+                                       den_eps, eps, _p(norm_w), (1 if norm_w.numel() == H * dv and H > 1 else 0),
+                                       _p(raw), _p(gate_buf), _p(out), dt(out), batch.S, T, _stream()), "mlstm_col_scan")
+        return
     _check(lib().nv_mlstm_scan(_p(proj), proj.stride(0), cols["q"], cols["k"], cols["v"], cols["g"], cols["i"],
                                cols["f"], _p(batch.cu_rows), _p(batch.entry_slot), _p(S), _slot_stride(S), _p(n),
                                _slot_stride(n), _p(m), _slot_stride(m), H, dk, dv, cap, float(dk) ** -0.5, den_eps,
@@ -798,12 +826,23 @@ def mlstm_scan(proj, cols: dict, batch, S, n, m, H: int, dk: int, dv: int, cap: 
 
 
 def gated_delta_scan(qkv, cols: dict, G: int, proj, pcols: dict, A_log, dt_bias, batch, S, H: int, dk: int, dv: int,
-                     eps: float, norm_w, out) -> None:
+                     eps: float, norm_w, out, *, columns: bool = True) -> None:
     """The gated delta rule, row by row per entry.  ``qkv`` float32 [T, C]: q, k, v after convolution and unit norm
-    at ``cols`` (q, k, v); ``proj``: output gate, beta and decay pre-activations at ``pcols`` (g, b, a)."""
+    at ``cols`` (q, k, v); ``proj``: output gate, beta and decay pre-activations at ``pcols`` (g, b, a).
+    ``columns`` as in ``mlstm_scan``."""
     _cuda_contig(qkv, A_log, dt_bias, norm_w, out)
     _f32(qkv, A_log, dt_bias, norm_w)
     _need(proj.stride(-1) == 1 and norm_w.numel() == dv and out.shape == (qkv.shape[0], H * dv), "gated_delta_scan: shapes")
+    if columns and col_scan_usable(dk, dv):
+        T = qkv.shape[0]
+        raw = torch.empty((T, H, dv), dtype=torch.float32, device=qkv.device)
+        gate_buf = torch.empty((T, H, 2), dtype=torch.float32, device=qkv.device)
+        _check(lib().nv_gated_delta_col_scan(_p(qkv), qkv.shape[1], cols["q"], cols["k"], cols["v"], G, _p(proj),
+                                             dt(proj), proj.stride(0), pcols["g"], pcols["b"], pcols["a"], _p(A_log),
+                                             _p(dt_bias), _p(batch.cu_rows), _p(batch.entry_slot), _p(S),
+                                             _slot_stride(S), H, dk, dv, eps, _p(norm_w), _p(raw), _p(gate_buf), _p(out),
+                                             dt(out), batch.S, T, _stream()), "gated_delta_col_scan")
+        return
     _check(lib().nv_gated_delta_scan(_p(qkv), qkv.shape[1], cols["q"], cols["k"], cols["v"], G, _p(proj), dt(proj),
                                      proj.stride(0), pcols["g"], pcols["b"], pcols["a"], _p(A_log), _p(dt_bias),
                                      _p(batch.cu_rows), _p(batch.entry_slot), _p(S), _slot_stride(S), H, dk, dv, eps,
@@ -820,15 +859,16 @@ def qk_prepare_store(src, q0: int, k0: int, v0: int, positions, row_entry, block
     _f32(q_weight, k_weight, inv_freq)
     T = src.shape[0]
     page = k_cache.shape[2]
-    _need(src.stride(-1) == 1 and q_out.shape == (T, Hq * D), "qk_prepare_store: shapes")
-    _need(k_cache.shape[1:] == (Hkv, page, D) and v_cache.shape[1:] == (Hkv, page, Dv) and k_cache.dtype == v_cache.dtype,
-          "qk_prepare_store: cache shapes")
+    QP, KP, VP = q_out.shape[1] // Hq, k_cache.shape[3], v_cache.shape[3]      # a head's elements, padded with zeros
+    _need(src.stride(-1) == 1 and q_out.shape == (T, Hq * QP) and QP >= D, "qk_prepare_store: shapes")
+    _need(k_cache.shape[1:3] == (Hkv, page) and v_cache.shape[1:3] == (Hkv, page) and KP >= D and VP >= Dv
+          and k_cache.dtype == v_cache.dtype, "qk_prepare_store: cache shapes")
     _need(rot_dim == 0 or inv_freq.numel() >= rot_dim // 2, "qk_prepare_store: inv_freq")
     _check(lib().nv_qk_prepare_store(_p(src), dt(src), src.stride(0), q0, k0, v0, _p(positions), _p(row_entry),
                                      _p(block_table), block_table.shape[1], _p(q_weight), _p(k_weight), eps,
                                      _p(inv_freq), rot_dim, (1 if interleaved else 0), amplitude, _p(q_out), dt(q_out),
                                      _p(k_cache), _p(v_cache), dt(k_cache), Hq, Hkv, D, Dv, page,
-                                     (1 if write_kv else 0), _p(err.t), T, _stream()), "qk_prepare_store")
+                                     (1 if write_kv else 0), _p(err.t), T, QP, KP, VP, _stream()), "qk_prepare_store")
 
 
 def paged_attention_general(q, k_cache, v_cache, block_table, row_entry, positions, scale: float, window: int, out,

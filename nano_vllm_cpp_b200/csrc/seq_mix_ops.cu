@@ -377,7 +377,9 @@ __global__ void __launch_bounds__(SM_THREADS) gated_delta_scan_kernel(DeltaArgs 
 // in: [T, ld] with q at q0 (Hq * D), k at k0 (Hkv * D), v at v0 (Hkv * Dv).  Per q and k head: RMS norm over D with
 // the weight qw / kw (null: no norm); then the first rot_dim elements are turned in pairs, (2i, 2i + 1) if
 // `interleaved` else (i, i + rot_dim / 2), by the angle position * inv_freq[i], cosine and sine times `amplitude`.
-// q goes to q_out [T, Hq * D]; k and v go to the row's place in their pages.  One block per row, a warp per head.
+// q goes to q_out [T, Hq * QP]; k and v go to the row's place in their pages, whose rows may be longer than D and
+// Dv (KP, VP): what lies behind a head's elements is written as zero, so that a kernel that wants one head size
+// for q, k and v can read all three.  One block per row, a warp per head.
 struct QkArgs {
   const void* in;
   int in_dt;
@@ -400,6 +402,7 @@ struct QkArgs {
   int cache_dt;
   int Hq, Hkv, D, Dv, page, write_kv;
   int* err;
+  int QP, KP, VP;           // elements per head in q_out, in the key pages and in the value pages (>= D, D, Dv; the rest is zero)
 };
 
 constexpr int QK_THREADS = 128;
@@ -446,18 +449,19 @@ __global__ void __launch_bounds__(QK_THREADS) qk_prepare_store_kernel(QkArgs a) 
     }
     __syncwarp();
     if (is_q) {
-      for (int i = lane; i < D; i += 32) st_dt(a.q_out, a.q_dt, (size_t)t * a.Hq * D + (size_t)h * D + i, buf[i]);
+      const size_t dst = ((size_t)t * a.Hq + h) * a.QP;
+      for (int i = lane; i < a.QP; i += 32) st_dt(a.q_out, a.q_dt, dst + i, i < D ? buf[i] : 0.f);
     } else {
-      const size_t dst = (((size_t)blk * a.Hkv + (h - a.Hq)) * a.page + slot) * D;
-      for (int i = lane; i < D; i += 32) st_dt(a.kc, a.cache_dt, dst + i, buf[i]);
+      const size_t dst = (((size_t)blk * a.Hkv + (h - a.Hq)) * a.page + slot) * a.KP;
+      for (int i = lane; i < a.KP; i += 32) st_dt(a.kc, a.cache_dt, dst + i, i < D ? buf[i] : 0.f);
     }
     __syncwarp();
   }
   if (write_kv) {
-    for (int i = threadIdx.x; i < a.Hkv * a.Dv; i += QK_THREADS) {
-      const int hv = i / a.Dv, d = i % a.Dv;
-      const size_t dst = (((size_t)blk * a.Hkv + hv) * a.page + slot) * a.Dv + d;
-      st_dt(a.vc, a.cache_dt, dst, ld_dt(a.in, a.in_dt, (size_t)t * a.ld + a.v0 + i));
+    for (int i = threadIdx.x; i < a.Hkv * a.VP; i += QK_THREADS) {
+      const int hv = i / a.VP, d = i % a.VP;
+      const size_t dst = (((size_t)blk * a.Hkv + hv) * a.page + slot) * a.VP + d;
+      st_dt(a.vc, a.cache_dt, dst, d < a.Dv ? ld_dt(a.in, a.in_dt, (size_t)t * a.ld + a.v0 + hv * a.Dv + d) : 0.f);
     }
   }
 }
@@ -528,6 +532,271 @@ __global__ void __launch_bounds__(ATTG_THREADS) paged_attention_general_kernel(
   const size_t ob = (size_t)t * Hq * Dv + (size_t)h * Dv;
   if (tid < Dv) st_dt(out, out_dt, ob + tid, o0 * inv);
   if (tid + ATTG_THREADS < Dv) st_dt(out, out_dt, ob + tid + ATTG_THREADS, o1 * inv);
+}
+
+// ------------------------------------------------------------------ the same memories, a column per thread
+// A column of the head's matrix (its dk rows) stays in one thread's registers while the entry's rows run: the
+// columns of either recurrence never meet, so a row costs one barrier (for q and k of the row, staged in shared
+// memory through a ring of asynchronous copies) and a few exchanges between the neighbouring lanes that hold the
+// column's rows, sixteen each.  The kernel waits on shared memory and on its own short chains more than it issues,
+// so it wants many warps on a multiprocessor: a block is two warps with eight to thirty-two columns; blocks along z share a head's columns, so a single sequence fills more multiprocessors and a
+// decode step's read of the states is spread over them.  The matrix LSTM's normaliser is one more column (whose
+// value is 1), and its product with q one more output.  What needs a whole head, the division by the normaliser,
+// the head's RMS norm and the output gate, follows in head_finish_kernel, a row and head per warp.
+// raw: [T, H, RW] float32, RW = dv (+ 2 for the matrix LSTM: n . q and the running maximum m behind the dv sums).
+constexpr int COL_THREADS = 64;
+constexpr int COL_ROWS = 16;                           // rows of a column that one thread holds: DK / 16 lanes share a column
+constexpr int COL_MAX_COLS = COL_THREADS / 2;          // columns of a block at most (DK = 32)
+
+struct ColArgs {
+  const int* cu_rows;
+  const int* entry_slot;
+  float* S;                 // [slots][H, dk, dv]
+  long long S_stride;
+  float* n;                 // matrix LSTM: [slots][H, dk]
+  long long n_stride;
+  float* m;                 // matrix LSTM: [slots][H]
+  long long m_stride;
+  const float* qk;          // rows that hold q and k: [T, qk_ld]
+  long long qk_ld;
+  int q0, k0, G;            // q/k head of value head h: h / (H / G)
+  const float* vsrc;        // rows that hold v: [T, v_ld]
+  long long v_ld;
+  int v0;
+  const void* gates;        // rows that hold the two per-head gate pre-activations: [T, gates_ld] float32
+  int gates_dt;
+  long long gates_ld;
+  int ga0, gb0;             // matrix LSTM: i, f; delta rule: beta, decay
+  const float* A_log;
+  const float* dt_bias;
+  float cap, q_scale;
+  float* raw;
+  int RW, H, dk, dv;
+};
+
+// The gates of a row and head, ready for the recurrence: the matrix LSTM's capped log gates (i, f), or the delta
+// rule's beta and decay.  For steps of many rows this runs over all rows at once before the scan (PRE), which then
+// only reads them; a step of few rows computes them in the scan itself and saves the launch.
+__device__ __forceinline__ void scan_gates(int mode, float ga, float gb, float cap, float rate, float dtb, float& x,
+                                           float& y) {
+  if (mode == 0) {
+    x = cap * tanhf(ga / cap);
+    y = logsigmoidf_(cap * tanhf(gb / cap));
+  } else {
+    x = sigmoidf_(ga);
+    y = expf(-rate * softplusf_(gb + dtb));
+  }
+}
+
+__global__ void scan_gates_kernel(const float* __restrict__ gates, long long ld, int ga0, int gb0, int H, int mode,
+                                  float cap, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                  float* __restrict__ out, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long t = i / H;
+  const int h = (int)(i % H);
+  float x, y;
+  scan_gates(mode, gates[t * ld + ga0 + h], gates[t * ld + gb0 + h], cap, mode ? expf(A_log[h]) : 0.f,
+             mode ? dt_bias[h] : 0.f, x, y);
+  out[2 * i] = x;
+  out[2 * i + 1] = y;
+}
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int COL_RING = 8;             // rows in flight: a row's q, k, v and gates are asked for this many rows ahead
+
+template <int DK, int MODE, bool PRE>   // MODE 0: matrix LSTM, 1: gated delta rule; PRE: the gates come ready
+__global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
+  // A ring of rows in shared memory, filled by asynchronous copies several rows ahead of the row that is computed:
+  // with one row ahead every row waited for its loads' way through the memory system.
+  __shared__ __align__(16) float qs[COL_RING][DK];
+  __shared__ __align__(16) float ks[COL_RING][DK];
+  constexpr int COL_RSPLIT = DK / COL_ROWS;          // lanes that share a column (2, 4 or 8)
+  constexpr int COL_COLS = COL_THREADS / COL_RSPLIT; // columns of a block
+  __shared__ float vs[COL_RING][COL_COLS];
+  __shared__ float gs[COL_RING][2];
+  constexpr int PER = DK / COL_THREADS > 0 ? DK / COL_THREADS : 1;
+  constexpr int DKH = COL_ROWS;                      // rows of a column that one thread holds
+  const int e = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int dk = a.dk, dv = a.dv;
+  const int gh = h / (a.H / a.G);
+  const int half = tid % COL_RSPLIT;                 // neighbouring lanes share a column, each a part of its rows
+  const int cl = tid / COL_RSPLIT;                   // the column's place in the block
+  const int c = blockIdx.z * COL_COLS + cl;
+  const int rbase = half * DKH;
+  const int ncols = MODE == 0 ? dv + 1 : dv;
+  const bool active = c < ncols;
+  const bool is_n = MODE == 0 && c == dv;
+  const int row0 = a.cu_rows[e], row1 = a.cu_rows[e + 1];
+  const int slot = a.entry_slot[e];
+  float* colp = nullptr;
+  long long cstride = 0;
+  if (active) {
+    if (is_n) { colp = a.n + (size_t)slot * a.n_stride + (size_t)h * dk; cstride = 1; }
+    else { colp = a.S + (size_t)slot * a.S_stride + (size_t)h * dk * dv + c; cstride = dv; }
+  }
+  float Sreg[DKH];
+#pragma unroll
+  for (int r = 0; r < DKH; ++r) Sreg[r] = (active && rbase + r < dk) ? colp[(size_t)(rbase + r) * cstride] : 0.f;
+  float m = 0.f, rate = 0.f, dtb = 0.f;
+  if (MODE == 0) m = a.m[(size_t)slot * a.m_stride + h];
+  else { rate = expf(a.A_log[h]); dtb = a.dt_bias[h]; }
+  // what no copy ever writes: the rows of q and k beyond dk, the value of the normaliser's column and of no column
+  for (int i = tid; i < COL_RING * DK; i += COL_THREADS)
+    if (i % DK >= dk) { qs[i / DK][i % DK] = 0.f; ks[i / DK][i % DK] = 0.f; }
+  if (half == 0 && !(active && !is_n))
+    for (int i = 0; i < COL_RING; ++i) vs[i][cl] = 1.f;
+  const float* gates = (const float*)a.gates;
+  const bool has_v = active && !is_n && half == 0;
+  auto fetch = [&](int t) {
+    if (t < row1) {
+      const int b = (t - row0) % COL_RING;
+      const float* x = a.qk + (size_t)t * a.qk_ld;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int r = tid + i * COL_THREADS;
+        if (r < dk && r < DK) {
+          cp_async4(&qs[b][r], x + a.q0 + gh * dk + r);
+          cp_async4(&ks[b][r], x + a.k0 + gh * dk + r);
+        }
+      }
+      if (has_v) cp_async4(&vs[b][cl], a.vsrc + (size_t)t * a.v_ld + a.v0 + h * dv + c);
+      if (tid < 2) cp_async4(&gs[b][tid], gates + (size_t)t * a.gates_ld + (tid ? a.gb0 : a.ga0) + (PRE ? 2 * h : h));
+    }
+    cp_async_commit();                               // (a group per row, also an empty one: the count below relies on it)
+  };
+  for (int j = 0; j < COL_RING - 1; ++j) fetch(row0 + j);
+  for (int t = row0; t < row1; ++t) {
+    const int b = (t - row0) % COL_RING;
+    cp_async_wait<COL_RING - 2>();                   // this thread's copies of row t have landed ...
+    __syncthreads();                                 // ... and everyone's; and everyone is done with row t - 1,
+    fetch(t + COL_RING - 1);                         // whose place in the ring the new row takes
+    const float v = vs[b][cl], ga = gs[b][0], gb = gs[b][1];
+    const float4* q4 = reinterpret_cast<const float4*>(qs[b] + rbase);
+    const float4* k4 = reinterpret_cast<const float4*>(ks[b] + rbase);
+    float* out = a.raw + ((size_t)t * a.H + h) * a.RW;
+    if (MODE == 0) {
+      float ig = ga, fg = gb;
+      if (!PRE) scan_gates(0, ga, gb, a.cap, 0.f, 0.f, ig, fg);
+      const float m_new = fmaxf(fg + m, ig);
+      const float fa = expf(fg + m - m_new), bv = expf(ig - m_new) * v;
+      m = m_new;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;          // four chains; added up in a fixed order
+#pragma unroll
+      for (int r4 = 0; r4 < DKH / 4; ++r4) {
+        const float4 qq = q4[r4], kk = k4[r4];
+        float s;
+        s = fmaf(fa, Sreg[4 * r4 + 0], kk.x * bv); Sreg[4 * r4 + 0] = s; a0 = fmaf(s, qq.x, a0);
+        s = fmaf(fa, Sreg[4 * r4 + 1], kk.y * bv); Sreg[4 * r4 + 1] = s; a1 = fmaf(s, qq.y, a1);
+        s = fmaf(fa, Sreg[4 * r4 + 2], kk.z * bv); Sreg[4 * r4 + 2] = s; a2 = fmaf(s, qq.z, a2);
+        s = fmaf(fa, Sreg[4 * r4 + 3], kk.w * bv); Sreg[4 * r4 + 3] = s; a3 = fmaf(s, qq.w, a3);
+      }
+      float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+      for (int off = 1; off < COL_RSPLIT; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);   // same sum in every lane
+      if (active && half == 0) out[c] = acc * a.q_scale;     // q's scale, taken out of the sum
+      if (blockIdx.z == 0 && tid == 0) out[dv + 1] = m;
+    } else {
+      float beta = ga, g = gb;
+      if (!PRE) scan_gates(1, ga, gb, 0.f, rate, dtb, beta, g);
+      float ak = 0.f, aq = 0.f, kq = 0.f, ak1 = 0.f, aq1 = 0.f, kq1 = 0.f;     // two chains each
+#pragma unroll
+      for (int r4 = 0; r4 < DKH / 4; ++r4) {
+        const float4 qq = q4[r4], kk = k4[r4];
+        ak = fmaf(Sreg[4 * r4 + 0], kk.x, ak); aq = fmaf(Sreg[4 * r4 + 0], qq.x, aq); kq = fmaf(kk.x, qq.x, kq);
+        ak1 = fmaf(Sreg[4 * r4 + 1], kk.y, ak1); aq1 = fmaf(Sreg[4 * r4 + 1], qq.y, aq1); kq1 = fmaf(kk.y, qq.y, kq1);
+        ak = fmaf(Sreg[4 * r4 + 2], kk.z, ak); aq = fmaf(Sreg[4 * r4 + 2], qq.z, aq); kq = fmaf(kk.z, qq.z, kq);
+        ak1 = fmaf(Sreg[4 * r4 + 3], kk.w, ak1); aq1 = fmaf(Sreg[4 * r4 + 3], qq.w, aq1); kq1 = fmaf(kk.w, qq.w, kq1);
+      }
+      ak += ak1; aq += aq1; kq += kq1;
+#pragma unroll
+      for (int off = 1; off < COL_RSPLIT; off <<= 1) {       // the column's lanes all get the same sums
+        ak += __shfl_xor_sync(0xffffffffu, ak, off);
+        aq += __shfl_xor_sync(0xffffffffu, aq, off);
+        kq += __shfl_xor_sync(0xffffffffu, kq, off);
+      }
+      const float u = beta * (v - g * ak);
+      if (active && half == 0) out[c] = fmaf(kq, u, g * aq) * a.q_scale;
+#pragma unroll
+      for (int r4 = 0; r4 < DKH / 4; ++r4) {
+        const float4 kk = k4[r4];
+        Sreg[4 * r4 + 0] = fmaf(g, Sreg[4 * r4 + 0], kk.x * u);
+        Sreg[4 * r4 + 1] = fmaf(g, Sreg[4 * r4 + 1], kk.y * u);
+        Sreg[4 * r4 + 2] = fmaf(g, Sreg[4 * r4 + 2], kk.z * u);
+        Sreg[4 * r4 + 3] = fmaf(g, Sreg[4 * r4 + 3], kk.w * u);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  if (active) {
+#pragma unroll
+    for (int r = 0; r < DKH; ++r)
+      if (rbase + r < dk) colp[(size_t)(rbase + r) * cstride] = Sreg[r];
+  }
+  if (MODE == 0 && blockIdx.z == 0 && tid == 0) a.m[(size_t)slot * a.m_stride + h] = m;
+}
+
+// A row and head per warp: o = raw (divided, for the matrix LSTM, by max(|n . q|, exp(-m)) + den_eps), then
+// o / sqrt(mean(o^2) + eps) * w * act(gate), act the sigmoid (gate_act 0) or silu (1).
+__global__ void __launch_bounds__(256) head_finish_kernel(const float* __restrict__ raw, int RW, int has_den,
+                                                          float den_eps, const void* __restrict__ gate, int gate_dt,
+                                                          long long gate_ld, int g0, int gate_act,
+                                                          const float* __restrict__ w, int w_per_head, float eps,
+                                                          void* __restrict__ out, int out_dt, int T, int H, int dv) {
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)T * H) return;
+  const int t = (int)(item / H), h = (int)(item % H);
+  const float* x = raw + (size_t)item * RW;
+  float inv = 1.f;
+  if (has_den) inv = 1.f / (fmaxf(fabsf(x[dv]), expf(-x[dv + 1])) + den_eps);
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) { const float o = x[i] * inv; ss = fmaf(o, o, ss); }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)dv + eps);
+  for (int i = lane; i < dv; i += 32) {
+    const float gv = ld_dt(gate, gate_dt, (size_t)t * gate_ld + g0 + h * dv + i);
+    const float act = gate_act == 0 ? sigmoidf_(gv) : siluf_(gv);
+    st_dt(out, out_dt, (size_t)t * H * dv + (size_t)h * dv + i, x[i] * inv * r * w[w_per_head ? h * dv + i : i] * act);
+  }
+}
+
+// Steps of more rows than this compute their gates in a pass of their own before the scan.
+constexpr int SCAN_GATES_APART_ROWS = 64;
+
+// `gate_buf`: [T, H, 2] float32 scratch for the gates (may be null for steps of few rows).
+template <int MODE, bool PRE>
+int launch_col_scan_p(const ColArgs& a, int S, cudaStream_t s) {
+  const int ncols = MODE == 0 ? a.dv + 1 : a.dv;
+  const int DKp = a.dk <= 32 ? 32 : (a.dk <= 64 ? 64 : 128);
+  const int cols = COL_THREADS / (DKp / COL_ROWS);   // columns of a block
+  dim3 grid(S, a.H, (ncols + cols - 1) / cols);
+  if (a.dk <= 32) col_scan_kernel<32, MODE, PRE><<<grid, COL_THREADS, 0, s>>>(a);
+  else if (a.dk <= 64) col_scan_kernel<64, MODE, PRE><<<grid, COL_THREADS, 0, s>>>(a);
+  else if (a.dk <= 128) col_scan_kernel<128, MODE, PRE><<<grid, COL_THREADS, 0, s>>>(a);
+  else return NV_ERR_UNSUPPORTED;
+  NV_RETURN_LAST();
+}
+
+template <int MODE>
+int launch_col_scan(ColArgs a, int S, int T, float* gate_buf, cudaStream_t s) {
+  if (T > SCAN_GATES_APART_ROWS && gate_buf) {
+    const long long n = (long long)T * a.H;
+    scan_gates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float*)a.gates, a.gates_ld, a.ga0, a.gb0, a.H,
+                                                                 MODE, a.cap, a.A_log, a.dt_bias, gate_buf, n);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    a.gates = gate_buf; a.gates_ld = 2LL * a.H; a.ga0 = 0; a.gb0 = 1;
+    return launch_col_scan_p<MODE, true>(a, S, s);
+  }
+  return launch_col_scan_p<MODE, false>(a, S, s);
 }
 
 size_t scan_smem(int dk, int dv, int parts) {
@@ -667,12 +936,14 @@ NV_API int nv_qk_prepare_store(const void* in, int in_dt, long long ld, int q0, 
                                const int* row_entry, const int* block_table, int max_blocks, const float* qw,
                                const float* kw, float eps, const float* inv_freq, int rot_dim, int interleaved,
                                float amplitude, void* q_out, int q_dt, void* kc, void* vc, int cache_dt, int Hq,
-                               int Hkv, int D, int Dv, int page, int write_kv, int* err, int T, cudaStream_t s) {
+                               int Hkv, int D, int Dv, int page, int write_kv, int* err, int T, int QP, int KP,
+                               int VP, cudaStream_t s) {
   if (!dt_ok(in_dt) || !dt_ok(q_dt) || !dt_ok(cache_dt)) return NV_ERR_BAD_DTYPE;
   if (rot_dim < 0 || rot_dim > D || rot_dim % 2 || D <= 0 || Dv <= 0) return NV_ERR_BAD_SIZE;
+  if (QP < D || KP < D || VP < Dv) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
   QkArgs a = {in, in_dt, ld, q0, k0, v0, positions, row_entry, block_table, max_blocks, qw, kw, eps, inv_freq, rot_dim,
-              interleaved, amplitude, q_out, q_dt, kc, vc, cache_dt, Hq, Hkv, D, Dv, page, write_kv, err};
+              interleaved, amplitude, q_out, q_dt, kc, vc, cache_dt, Hq, Hkv, D, Dv, page, write_kv, err, QP, KP, VP};
   const size_t smem = sizeof(float) * (size_t)(QK_THREADS / 32) * D;
   int rc = allow_smem(qk_prepare_store_kernel, smem);
   if (rc) return rc;
@@ -692,5 +963,53 @@ NV_API int nv_paged_attention_general(const void* q, int q_dt, const void* kc, c
                                                                       max_blocks, row_entry, positions, scale, window,
                                                                       has_sink, sink_score, out, out_dt, Hq, Hkv, D,
                                                                       Dv, page);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_col_scan_usable(int dk, int dv) { return dk >= 1 && dk <= 128 && dv >= 1; }
+
+// The matrix LSTM through col_scan_kernel; raw: [T, H, dv + 2] and gate_buf: [T, H, 2] float32 scratch.
+NV_API int nv_mlstm_col_scan(const float* proj, long long ld, int q0, int k0, int v0, int g0, int i0, int f0,
+                             const int* cu_rows, const int* entry_slot, float* S, long long S_stride, float* n,
+                             long long n_stride, float* m, long long m_stride, int H, int dk, int dv, float cap,
+                             float q_scale, float den_eps, float eps, const float* norm_w, int norm_per_head,
+                             float* raw, float* gate_buf, void* out, int out_dt, int num_entries, int T,
+                             cudaStream_t s) {
+  if (!dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (!nv_col_scan_usable(dk, dv) || H <= 0) return NV_ERR_UNSUPPORTED;
+  if (num_entries == 0 || T == 0) return NV_OK;
+  ColArgs a = {};
+  a.cu_rows = cu_rows; a.entry_slot = entry_slot; a.S = S; a.S_stride = S_stride; a.n = n; a.n_stride = n_stride;
+  a.m = m; a.m_stride = m_stride; a.qk = proj; a.qk_ld = ld; a.q0 = q0; a.k0 = k0; a.G = H; a.vsrc = proj; a.v_ld = ld;
+  a.v0 = v0; a.gates = proj; a.gates_dt = NV_DT_F32; a.gates_ld = ld; a.ga0 = i0; a.gb0 = f0; a.cap = cap;
+  a.q_scale = q_scale; a.raw = raw; a.RW = dv + 2; a.H = H; a.dk = dk; a.dv = dv;
+  int rc = launch_col_scan<0>(a, num_entries, T, gate_buf, s);
+  if (rc) return rc;
+  const long long items = (long long)T * H;
+  head_finish_kernel<<<(unsigned)((items + 7) / 8), 256, 0, s>>>(raw, dv + 2, 1, den_eps, proj, NV_DT_F32, ld, g0, 0,
+                                                                 norm_w, norm_per_head, eps, out, out_dt, T, H, dv);
+  NV_RETURN_LAST();
+}
+
+// The gated delta rule through col_scan_kernel; raw: [T, H, dv] and gate_buf: [T, H, 2] float32 scratch.
+NV_API int nv_gated_delta_col_scan(const float* qkv, int C, int q0, int k0, int v0, int G, const void* proj,
+                                   int proj_dt, long long ld, int g0, int b0, int a0, const float* A_log,
+                                   const float* dt_bias, const int* cu_rows, const int* entry_slot, float* S,
+                                   long long S_stride, int H, int dk, int dv, float eps, const float* norm_w,
+                                   float* raw, float* gate_buf, void* out, int out_dt, int num_entries, int T,
+                                   cudaStream_t s) {
+  if (!dt_ok(out_dt) || proj_dt != NV_DT_F32) return NV_ERR_BAD_DTYPE;
+  if (!nv_col_scan_usable(dk, dv) || H <= 0 || G <= 0 || H % G) return NV_ERR_UNSUPPORTED;
+  if (num_entries == 0 || T == 0) return NV_OK;
+  ColArgs a = {};
+  a.cu_rows = cu_rows; a.entry_slot = entry_slot; a.S = S; a.S_stride = S_stride; a.qk = qkv; a.qk_ld = C; a.q0 = q0;
+  a.k0 = k0; a.G = G; a.vsrc = qkv; a.v_ld = C; a.v0 = v0; a.gates = proj; a.gates_dt = proj_dt; a.gates_ld = ld;
+  a.ga0 = b0; a.gb0 = a0; a.A_log = A_log; a.dt_bias = dt_bias; a.q_scale = 1.f; a.raw = raw; a.RW = dv; a.H = H;
+  a.dk = dk; a.dv = dv;
+  int rc = launch_col_scan<1>(a, num_entries, T, gate_buf, s);
+  if (rc) return rc;
+  const long long items = (long long)T * H;
+  head_finish_kernel<<<(unsigned)((items + 7) / 8), 256, 0, s>>>(raw, dv, 0, 0.f, proj, proj_dt, ld, g0, 1, norm_w, 0,
+                                                                 eps, out, out_dt, T, H, dv);
   NV_RETURN_LAST();
 }

@@ -85,11 +85,23 @@ class PagedAttention(Mixer):
             self.qkv_bias = _cat([fetch(n["q_bias"]), fetch(n["k_bias"]), fetch(n["v_bias"])])
         self.o_weight = fetch(n["o"])
         self.o_bias = fetch(n["o_bias"]) if self.out_bias else None
+        # The tensor-core kernel wants one head size for q, k and v, a multiple of 16: a bfloat16 run of the general
+        # path pads the three with zeros up to it (the scores and the sums are the same), and the output
+        # projection gets zero columns for the padding.
+        self.pad = 0
+        if self.general and ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and self.o_weight.dtype == torch.bfloat16:
+            self.pad = (max(self.D, self.Dv) + 15) // 16 * 16
+            if self.pad != self.Dv:
+                w = torch.zeros((self.hidden, self.Hq, self.pad), dtype=self.o_weight.dtype, device=self.o_weight.device)
+                w[:, :, :self.Dv] = self.o_weight.view(self.hidden, self.Hq, self.Dv)
+                self.o_weight = w.view(self.hidden, self.Hq * self.pad)
         self.q_norm = self.k_norm = None
         if self.qk_norm_eps is not None:
             self.q_norm, self.k_norm = fetch(n["q_norm"]), fetch(n["k_norm"])
 
     def cache_spec(self):
+        if getattr(self, "pad", 0):
+            return KVCacheSpec(self.Hkv, self.pad, self.window)
         return KVCacheSpec(self.Hkv, self.D, self.window, 0 if self.Dv == self.D else self.Dv)
 
     # ------------------------------------------------------------------ forward
@@ -114,15 +126,32 @@ class PagedAttention(Mixer):
         Hq, Hkv, D, Dv = self.Hq, self.Hkv, self.D, self.Dv
         proj = linear(ctx, h, self.qkv_weight, torch.float32, bias=self.qkv_bias)
         bt = batch.block_tables[cache.group]
-        q = torch.empty((T, Hq * D), dtype=ctx.act_dtype, device=h.device)
+        P = self.pad
+        q = torch.empty((T, Hq * (P or D)), dtype=ctx.act_dtype, device=h.device)
         pos = self.position
         ops.qk_prepare_store(proj, 0, Hq * D, (Hq + Hkv) * D, batch.positions, batch.row_entry, bt, self.q_norm,
                              self.k_norm, self.qk_norm_eps or 0.0, pos.inv_freq(), pos.rotary_dim,
                              pos.pairing == "interleaved", pos.amplitude, q, cache.k, cache.v, Hq, Hkv, D, Dv,
                              cache.write, ctx.err)
-        att = torch.empty((T, Hq * Dv), dtype=ctx.act_dtype, device=h.device)
-        ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale, self.window,
-                                    att, Hq, Hkv, D, Dv, sink_score=self.sink_score)
+        att = torch.empty((T, Hq * (P or Dv)), dtype=ctx.act_dtype, device=h.device)
+        if P:
+            # Entries of one row go to the split-key decode kernel (its form that keeps the weights float32), the
+            # others to the tensor-core kernel, where the float32 weights enter the product with the values as three
+            # bfloat16 terms; both add the sink to the softmax's denominator.
+            single = batch.n_single if ops.attention_decode_usable(cache.k, P) else 0
+            if single:
+                ops.attention_decode(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale, self.window,
+                                     att, Hq, Hkv, P, batch.max_context if batch.decode_only else batch.max_single_context,
+                                     rows=None if batch.decode_only else batch.single_rows, err=ctx.err,
+                                     sink_score=self.sink_score, float_weights=True)
+            if single < batch.S:
+                tiles = (batch.T - single) // ops.attention_prefill_tile_rows() + (batch.S - single)
+                ops.attention_prefill(q, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
+                                      self.window, att, Hq, Hkv, P, err=ctx.err, kernel="mma", min_rows=2 if single else 1,
+                                      sink_score=self.sink_score, weight_terms=3)
+        else:
+            ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
+                                        self.window, att, Hq, Hkv, D, Dv, sink_score=self.sink_score)
         return linear(ctx, att, self.o_weight, torch.float32, bias=self.o_bias)
 
     def _attend(self, qkv, cache, bt, batch, att):

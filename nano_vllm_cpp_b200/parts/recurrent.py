@@ -69,7 +69,8 @@ class MatrixLSTM(Mixer):
         proj = linear(ctx, h, self.w_in, torch.float32, bias=self.b_in)
         S, n, m = (p.state for p in cache.parts)
         y = torch.empty((h.shape[0], self.H * self.dv), dtype=ctx.act_dtype, device=h.device)
-        ops.mlstm_scan(proj, self.cols, batch, S, n, m, self.H, self.dk, self.dv, self.cap, self.eps, self.norm, y)
+        ops.mlstm_scan(proj, self.cols, batch, S, n, m, self.H, self.dk, self.dv, self.cap, self.eps, self.norm, y,
+                       columns=ctx.fast_kernels)
         return linear(ctx, y, self.w_out, torch.float32)
 
 
@@ -140,7 +141,7 @@ class GatedDeltaRule(Mixer):
             ops.conv_state_update(proj, 0, self.C, self.taps, batch, tail)
         y = torch.empty((T, H * dv), dtype=ctx.act_dtype, device=h.device)
         ops.gated_delta_scan(qkv, self.cols, G, proj, self.pcols, self.A_log, self.dt_bias, batch, S, H, dk, dv,
-                             self.eps, self.norm, y)
+                             self.eps, self.norm, y, columns=ctx.fast_kernels)
         return linear(ctx, y, self.w_out, torch.float32)
 
 

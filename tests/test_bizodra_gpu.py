@@ -106,10 +106,10 @@ class Steps:
 
 
 # ------------------------------------------------------------------------------- the parts alone
-def ctx_for(dtype):
+def ctx_for(dtype, fast=True):
     from nano_vllm_cpp_b200.csrc import ops
     from nano_vllm_cpp_b200.parts import RunContext
-    return RunContext(device=torch.device(DEV), act_dtype=dtype, err=ops.ErrorFlag(DEV), page_size=16)
+    return RunContext(device=torch.device(DEV), act_dtype=dtype, err=ops.ErrorFlag(DEV), page_size=16, fast_kernels=fast)
 
 
 class Fetch:
@@ -160,11 +160,11 @@ CUTS = [[(0, 37), (0, 2)], [(37, 38), (2, 19)], [(38, 40), (19, 20)], [(40, 41),
         [(41, 64), (50, 51)]]
 
 
-def part_setup(kind, params, tensors, dtype, prefix="m."):
+def part_setup(kind, params, tensors, dtype, prefix="m.", fast=True):
     from nano_vllm_cpp_b200.parts import build_part, PartSpec
     from nano_vllm_cpp_b200.cache import DeviceCache
     part = build_part("mixer", PartSpec(kind, params))
-    ctx = ctx_for(dtype)
+    ctx = ctx_for(dtype, fast)
     part.load(Fetch(tensors, prefix, dtype), ctx)
     cache = DeviceCache([part.cache_spec()], 16, 4, DEV, dtype)
     cache.allocate(24, 32)
@@ -182,13 +182,17 @@ def inputs(width, lengths, seed):
     return [torch.randn(n, width, generator=g).to(torch.bfloat16).double() for n in lengths]
 
 
+@pytest.mark.parametrize("fast", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("m", [LSTM_A, LSTM_B, {"heads": 2, "dim": 72, "vdim": 136, "gate_cap": 5.0}])
-def test_matrix_lstm_alone(dtype, m):
+@pytest.mark.parametrize("m", [LSTM_A, LSTM_B, {"heads": 2, "dim": 72, "vdim": 136, "gate_cap": 5.0},
+                               {"heads": 1, "dim": 136, "vdim": 24, "gate_cap": 8.0}])
+def test_matrix_lstm_alone(dtype, m, fast):
+    """``fast``: the kernel that keeps a column of the matrix per thread (keys up to 128 long; beyond that, and
+    without ``fast``, the kernel that keeps the matrix in shared memory)."""
     width, eps = 80, 1e-5
     W = mixer_weights({"type": "mlstm", "mixer": m}, width, 11)
     part, cache, ctx = part_setup("matrix_lstm", dict(hidden_size=width, heads=m["heads"], dim=m["dim"], vdim=m["vdim"],
-                                                      gate_cap=m["gate_cap"], eps=eps), W, dtype)
+                                                      gate_cap=m["gate_cap"], eps=eps), W, dtype, fast=fast)
     xs = inputs(width, [64, 51], 12)
     got = run_cut(part, cache, xs, CUTS, dtype, [[], []], ctx, slots=[2, 0])
     for i, x in enumerate(xs):
@@ -209,24 +213,27 @@ def test_matrix_lstm_large_gates_and_first_rows():
     close(got[0], pb.matrix_lstm(xs[0], W, "m.", m, eps), 1e-4, "rows")
 
 
+@pytest.mark.parametrize("fast", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("m", [RIGHT_A, RIGHT_B, {"heads": 6, "kv_heads": 3, "dim": 40, "vdim": 72, "conv": 5},
-                               {"heads": 2, "kv_heads": 2, "dim": 16, "vdim": 16, "conv": 1}])
-def test_gated_delta_alone(dtype, m):
+                               {"heads": 2, "kv_heads": 2, "dim": 16, "vdim": 16, "conv": 1},
+                               {"heads": 2, "kv_heads": 1, "dim": 128, "vdim": 136, "conv": 4}])
+def test_gated_delta_alone(dtype, m, fast):
     """Portions shorter than the convolution's reach (one and two rows), so that its kept inputs are a mix of old
     and new ones."""
     width, eps = 80, 1e-5
     W = mixer_weights({"type": "parallel", "mixer": {"left": LEFT_A, "right": m}}, width, 21)
     W = {k.replace("m.right.", "m."): v for k, v in W.items() if k.startswith("m.right.")}
     part, cache, ctx = part_setup("gated_delta_rule", dict(hidden_size=width, heads=m["heads"], kv_heads=m["kv_heads"],
-                                                           dim=m["dim"], vdim=m["vdim"], conv=m["conv"], eps=eps), W, dtype)
+                                                           dim=m["dim"], vdim=m["vdim"], conv=m["conv"], eps=eps), W, dtype,
+                                  fast=fast)
     xs = inputs(width, [64, 51], 22)
     got = run_cut(part, cache, xs, CUTS, dtype, [[], []], ctx, slots=[1, 3])
     for i, x in enumerate(xs):
         close(got[i], pb.gated_delta(x, W, "m.", m, eps), TOL["float32"] if dtype == torch.float32 else 3e-2, f"request {i}")
 
 
-def attention_part(m, width, eps, W, dtype):
+def attention_part(m, width, eps, W, dtype, fast=True):
     from nano_vllm_cpp_b200.parts import PartSpec
     names = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b", "o_bias": "o.b",
              "q_norm": "q.norm", "k_norm": "k.norm"}
@@ -234,17 +241,19 @@ def attention_part(m, width, eps, W, dtype):
         hidden_size=width, num_heads=m["heads"], num_kv_heads=m["kv_heads"], head_dim=m["dim"], v_head_dim=m["vdim"],
         bias=True, out_bias=True, qk_norm_eps=eps, scale=m["scale"], sink_score=0.0, names=names,
         position=PartSpec("rotary_interleaved", dict(rotary_dim=m["rot"]["dims"], theta=m["rot"]["base"],
-                                                     scaling=m["rot"].get("scaling")))), W, dtype)
+                                                     scaling=m["rot"].get("scaling")))), W, dtype, fast=fast)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("m", [LEFT_A, LEFT_B, {"heads": 2, "kv_heads": 1, "dim": 128, "vdim": 128, "scale": 0.1,
                                                 "rot": {"dims": 64, "base": 1e6}}])
-def test_sink_attention_alone(dtype, m):
+@pytest.mark.parametrize("fast", [True, False])
+def test_sink_attention_alone(dtype, m, fast):
+    """``fast`` in bfloat16: the tensor-core kernel over heads padded to one size; else the general kernel."""
     width, eps = 80, 1e-5
     W = mixer_weights({"type": "parallel", "mixer": {"left": m, "right": RIGHT_B}}, width, 31)
     W = {k.replace("m.left.", "m."): v for k, v in W.items() if k.startswith("m.left.")}
-    part, cache, ctx = attention_part(m, width, eps, W, dtype)
+    part, cache, ctx = attention_part(m, width, eps, W, dtype, fast)
     xs = inputs(width, [64, 51], 32)
     got = run_cut(part, cache, xs, CUTS, dtype, [[7, 2, 9, 4], [0, 5, 11, 3]], ctx)
     for i, x in enumerate(xs):
