@@ -209,6 +209,9 @@ DESIGN_SIZES = {
 }
 
 
+PROMPTS_TOGETHER = 8
+
+
 def bizodra_config(z):
     W, H, G, D = z["width"], z["heads"], z["kv_heads"], z["dim"]
     lstm = {"heads": H, "dim": D, "vdim": D, "gate_cap": 15.0}
@@ -278,6 +281,18 @@ def design_bench(args) -> int:
             ms = timed(prefill, 3)
             row = {"size": size, "model": model, "params_m": round(params / 1e6, 1),
                    "prefill": {"tokens": T, "ms": round(ms, 3), "tokens_per_s": round(T / ms * 1e3, 1)}, "decode": []}
+            # several prompts in one step, as a scheduler under load makes them
+            many = [torch.randint(0, V, (T,), generator=g).tolist() for _ in range(PROMPTS_TOGETHER)]
+
+            def prefill_many():
+                runner.step([StepEntry(f"pm{i}", p, [T - 1]) for i, p in enumerate(many)], check=False)
+                for i in range(len(many)):
+                    runner.close(f"pm{i}")
+            for _ in range(2):
+                prefill_many()
+            ms = timed(prefill_many, 3)
+            row["prefill_together"] = {"prompts": len(many), "tokens": T * len(many), "ms": round(ms, 3),
+                                       "tokens_per_s": round(T * len(many) / ms * 1e3, 1)}
             # the prompt's kernels one by one (outside graphs, an event between any two)
             graphs, runner.cuda_graphs = runner.cuda_graphs, False
             with ops.KernelTimes() as kt:

@@ -1,7 +1,8 @@
 """Typed view of a Bizodra ``config.json``.
 
 The file lists its layers one by one: ``layers[i] = {"type", "mixer", "mlp"}``.  ``type`` names the mixer
-(``mlstm`` and ``mlstm_2``: a matrix LSTM; ``parallel``: softmax attention with a sink beside a gated delta rule),
+(``mlstm``: a matrix LSTM; ``parallel``: softmax attention with a sink beside a gated delta rule; a numeric suffix,
+as in ``mlstm_2``, marks a further set of sizes of the same kind),
 ``mixer`` holds the mixer's sizes and constants, ``mlp`` the feed-forward (``{"kind": "dense", "ff": n}``) or null.
 Top level: ``vocab``, ``width``, ``norm.eps``, ``token_side.dim`` (the per-layer token input; absent: none).
 Every size and constant is read from the file; a missing key, a wrong type or an unknown kind is an error that
@@ -105,7 +106,8 @@ class SinkAttentionConfig:
                   _positive(_need(d, "kv_heads", int, where), where + ".kv_heads"),
                   _positive(_need(d, "dim", int, where), where + ".dim"),
                   _positive(_need(d, "vdim", int, where), where + ".vdim"), _need(d, "scale", float, where),
-                  RotaryConfig.from_dict(_need(d, "rot", dict, where), where + ".rot"))
+                  RotaryConfig.from_dict(d["rot"], where + ".rot") if d.get("rot") is not None
+                  else RotaryConfig(0, 10000.0, None))          # no 'rot': nothing is turned
         if out.heads % out.kv_heads:
             raise ConfigError(f"config.json: '{where}.heads' must be a multiple of '{where}.kv_heads'")
         if out.rot.dims > out.dim:
@@ -144,7 +146,17 @@ class ParallelConfig:
                    GatedDeltaConfig.from_dict(_need(d, "right", dict, where), where + ".right"))
 
 
-MIXER_TYPES = {"mlstm": MatrixLstmConfig, "mlstm_2": MatrixLstmConfig, "parallel": ParallelConfig}
+MIXER_KINDS = {"mlstm": MatrixLstmConfig, "parallel": ParallelConfig}
+
+
+def mixer_kind(layer_type: str):
+    """The mixer a layer's ``type`` names.  A file numbers the second, third ... set of sizes of a kind
+    (``mlstm_2``): the kind is the name without that suffix."""
+    base = layer_type
+    head, sep, tail = layer_type.rpartition("_")
+    if sep and tail.isdigit() and head:
+        base = head
+    return MIXER_KINDS.get(base)
 
 
 @dataclass
@@ -179,17 +191,19 @@ class BizodraConfig:
         for i, L in enumerate(layers_raw):
             where = f"layers[{i}]"
             typ = _need(L, "type", str, where)
-            if typ not in MIXER_TYPES:
-                raise ConfigError(f"config.json: '{where}.type' is {typ!r}; known: {', '.join(sorted(MIXER_TYPES))}")
-            mixer = MIXER_TYPES[typ].from_dict(_need(L, "mixer", dict, where), where + ".mixer")
+            kind = mixer_kind(typ)
+            if kind is None:
+                raise ConfigError(f"config.json: '{where}.type' is {typ!r}; known: {', '.join(sorted(MIXER_KINDS))} "
+                                  "(with a numeric suffix for further sets of sizes, as in mlstm_2)")
+            mixer = kind.from_dict(_need(L, "mixer", dict, where), where + ".mixer")
             mlp = L.get("mlp")
-            kind, ff = None, 0
+            mlp_kind, ff = None, 0
             if mlp is not None:
-                kind = _need(mlp, "kind", str, where + ".mlp")
-                if kind != "dense":
-                    raise ConfigError(f"config.json: '{where}.mlp.kind' is {kind!r}; known: dense")
+                mlp_kind = _need(mlp, "kind", str, where + ".mlp")
+                if mlp_kind != "dense":
+                    raise ConfigError(f"config.json: '{where}.mlp.kind' is {mlp_kind!r}; known: dense")
                 ff = _positive(_need(mlp, "ff", int, where + ".mlp"), where + ".mlp.ff")
-            layers.append(BizodraLayer(typ, mixer, kind, ff))
+            layers.append(BizodraLayer(typ, mixer, mlp_kind, ff))
         side = d.get("token_side")
         side_dim = 0
         if side is not None:

@@ -63,6 +63,19 @@ __device__ __forceinline__ float warp_max(float v) {
 // SiLU(g) * u exactly as the reference writes it: g / (1 + expf(-g)) * u  (src/hip_ops.hip:419-429).
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+// What a product's launcher takes in its `swiglu` argument: 0 nothing, 1 the SwiGLU pairing of gate and up rows, or a
+// unary activation of every output value (after the bias): 2 gelu in its erf form, 3 gelu in its tanh form, 4 silu.
+#define NV_EPI_SWIGLU 1
+#define NV_EPI_GELU_ERF 2
+#define NV_EPI_GELU_TANH 3
+#define NV_EPI_SILU 4
+__device__ __forceinline__ float epilogue_act(int act, float v) {
+  if (act == 0) return v;
+  if (act == NV_EPI_GELU_ERF) return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+  if (act == NV_EPI_GELU_TANH) return 0.5f * v * (1.f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
+  return v / (1.f + expf(-v));
+}
+
 // Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may start
 // while the kernel before it in the stream still runs; what it reads of that kernel's results, and whatever it
 // writes, must come after grid_dep_wait(), which returns once the earlier kernel has finished and its writes

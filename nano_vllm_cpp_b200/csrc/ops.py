@@ -302,8 +302,21 @@ def add_rmsnorm(x, branch, w, eps: float, out, out32=None, *, mix=None) -> None:
 ADD_RMSNORM_MAX_MIX = 64
 
 
-def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles=None) -> None:
-    """out[m, :] = a[a_rows[m] or m, :] @ w.T (+ bias), or silu(gate) * up with ``swiglu``.
+EPILOGUE_ACTS = {"gelu_erf": 2, "gelu_tanh": 3, "silu": 4}
+
+
+def _epilogue(swiglu: bool, act) -> int:
+    """What the products' launchers take in their ``swiglu`` argument: 0 nothing, 1 the SwiGLU pairing, or the code
+    of a unary activation that every output value passes after the bias."""
+    if act is None:
+        return 1 if swiglu else 0
+    _need(not swiglu and act in EPILOGUE_ACTS, f"a product's activation is one of {sorted(EPILOGUE_ACTS)} and excludes swiglu")
+    return EPILOGUE_ACTS[act]
+
+
+def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles=None, act=None) -> None:
+    """out[m, :] = a[a_rows[m] or m, :] @ w.T (+ bias), or silu(gate) * up with ``swiglu``, or with ``act``
+    (gelu_erf, gelu_tanh, silu) that function of every value.
 
     ``tiles`` = (tile_expert, tile_row0, tile_rows, num_tiles) selects the grouped form, where w is
     [E, rows, K]."""
@@ -334,7 +347,7 @@ def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles
                                _p(w), dt(w), stride,
                                _p(bias), (dt(bias) if bias is not None else 0),
                                _p(out), dt(out), out.stride(0),
-                               M, N, K, (1 if swiglu else 0),
+                               M, N, K, _epilogue(swiglu, act),
                                _p(te), _p(tr0), _p(tr), _p(nt), max_tiles, _stream()), "gemm_plain")
 
 
@@ -925,7 +938,7 @@ def skinny_usable(a, w, rows: int, swiglu: bool = False) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, err=None) -> None:
+def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, err=None, act=None) -> None:
     """``out[:rows] = a[:rows] @ w.T (+ bias)`` for at most 32 rows (8 with ``swiglu``; default: all rows of ``a``),
     by streaming ``w`` once; ``swiglu`` as in ``gemm_plain``."""
     _cuda_contig(w, bias)
@@ -939,7 +952,7 @@ def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, err=None) -> N
     _need(bias is None or (not swiglu and bias.numel() == N), "skinny product: bias")
     _check(lib().nv_skinny_gemm(_p(a), a.stride(0), R, _p(w), N, K,
                                 _p(bias), (dt(bias) if bias is not None else 0), _p(out), dt(out),
-                                out.stride(0), (1 if swiglu else 0), _stream()),
+                                out.stride(0), _epilogue(swiglu, act), _stream()),
            f"skinny_gemm N={rows_w} K={K}", 0.0, float(w.element_size() * rows_w * K))
 
 
@@ -966,7 +979,7 @@ def permute_rows(src, rows, R=None):
     return dst
 
 
-def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=None, splits=None) -> None:
+def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=None, splits=None, act=None) -> None:
     """Tensor-core form of ``gemm_plain`` (dense)."""
     if a_rows is not None:
         a = permute_rows(a, a_rows, M)
@@ -983,7 +996,7 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
         scratch = torch.empty((splits, M, 2 * N if swiglu else N), dtype=torch.float32, device=a.device)
     _check(L.nv_tc_gemm(_p(a), a.stride(0), M, _p(w), rows_w, N, K,
                         _p(bias), (dt(bias) if bias is not None else 0), _p(out), dt(out),
-                        out.stride(0), (1 if swiglu else 0), n_tile, splits,
+                        out.stride(0), _epilogue(swiglu, act), n_tile, splits,
                         _p(scratch), _p(None), _p(None), _p(None), _p(None), 0, 0,
                         _p(err.t if err is not None else _global_err().t), _early(), 0, 0,
                         0, _p(None), 0, _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,

@@ -33,6 +33,7 @@ struct GemmArgs {
   int M, N, K;
   int bias_dt, out_dt;
   int swiglu;
+  int act;                  // unary activation of the outputs (0: none; NV_EPI_* codes)
 };
 
 template <typename TA, typename TW, bool SWIGLU>
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(GemmArgs g) {
       float v = acc[i][j];
       if (SWIGLU) v = silu_mul(v, acc2[i][j]);
       if (g.bias) v += ld_dt(g.bias, g.bias_dt, n);
-      st_dt(g.out, g.out_dt, orow + n, v);
+      st_dt(g.out, g.out_dt, orow + n, epilogue_act(g.act, v));
     }
   }
 }
@@ -152,8 +153,11 @@ NV_API int nv_gemm_plain(const void* A, int a_dt, long long lda, const int* a_ro
                          const int* tile_expert, const int* tile_row0, const int* tile_rows,
                          const int* num_tiles, int max_tiles, cudaStream_t stream) {
   if (!dt_ok(a_dt) || !dt_ok(w_dt) || !dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
-  if (M < 0 || N <= 0 || K <= 0) return NV_ERR_BAD_SIZE;
+  if (M < 0 || N <= 0 || K <= 0 || swiglu < 0 || swiglu > NV_EPI_SILU) return NV_ERR_BAD_SIZE;
+  const int act = swiglu >= 2 ? swiglu : 0;
+  swiglu = swiglu == NV_EPI_SWIGLU;
   GemmArgs g;
+  g.act = act;
   g.A = A; g.W = W; g.bias = bias; g.out = out; g.a_rows = a_rows;
   g.tile_expert = tile_expert; g.tile_row0 = tile_row0; g.tile_rows = tile_rows; g.num_tiles = num_tiles;
   g.lda = lda; g.ldo = ldo; g.w_expert_stride = w_expert_stride;

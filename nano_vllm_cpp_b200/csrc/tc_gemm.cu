@@ -59,6 +59,7 @@ struct TcArgs {
   int rows_per_expert;  // rows of W per expert (grouped), N or 2N
   int k_steps_total, k_steps_per_split, splits;
   int n_tile, swiglu, dual, stages;   // swiglu and dual both mean two weight tiles per stage
+  int act;                            // unary activation of the outputs after the bias (0: none; NV_EPI_* codes)
   int w_per_cta;                      // output features per CTA: 128, or 256 with dual
   int n_blocks;                       // blocks of w_per_cta features
   int acc_bufs;                       // accumulator sets in TMEM: 2 when two fit, else 1
@@ -170,8 +171,8 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
     for (int j = 0; j < W; ++j) {
       if (j < valid) {
         const float v = (a.swiglu ? silu_mul(g[j], u[j]) : g[j]) + bias;
-        st_dt(a.out, a.out_dt, (row + j) * a.ldo + n, v);
-        if (n2_ok) st_dt(a.out, a.out_dt, (row + j) * a.ldo + n2, u[j] + bias2);
+        st_dt(a.out, a.out_dt, (row + j) * a.ldo + n, epilogue_act(a.act, v));
+        if (n2_ok) st_dt(a.out, a.out_dt, (row + j) * a.ldo + n2, epilogue_act(a.act, u[j] + bias2));
       }
     }
     return;
@@ -184,6 +185,13 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
   for (int j = 0; j < W; ++j) {
     g[j] += bias;
     u[j] += bias2;
+  }
+  if (a.act) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      g[j] = epilogue_act(a.act, g[j]);
+      u[j] = epilogue_act(a.act, u[j]);
+    }
   }
   if (a.out_dt == NV_DT_BF16) {
     bf16* o = (bf16*)a.out + row * a.ldo;
@@ -454,8 +462,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               if (n2_ok) p[n2] = u[j];
             } else {
               float v = a.swiglu ? silu_mul(g[j], u[j]) : g[j];
-              st_dt(a.out, a.out_dt, row * a.ldo + n, v + bias);
-              if (n2_ok) st_dt(a.out, a.out_dt, row * a.ldo + n2, u[j] + bias2);
+              st_dt(a.out, a.out_dt, row * a.ldo + n, epilogue_act(a.act, v + bias));
+              if (n2_ok) st_dt(a.out, a.out_dt, row * a.ldo + n2, epilogue_act(a.act, u[j] + bias2));
             }
           }
         }
@@ -476,6 +484,8 @@ __global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int spl
                                       long long ldo) {
   grid_dep_wait();
   grid_dep_launch();
+  const int act = swiglu >= 2 ? swiglu : 0;          // (the argument's codes: common.cuh)
+  swiglu = swiglu == NV_EPI_SWIGLU;
   const int width = swiglu ? 2 * N : N;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)M_tok * N) return;
@@ -489,7 +499,7 @@ __global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int spl
   }
   float v = swiglu ? silu_mul(g, u) : g;
   if (bias) v += ld_dt(bias, bias_dt, n);
-  st_dt(out, out_dt, t * ldo + n, v);
+  st_dt(out, out_dt, t * ldo + n, epilogue_act(act, v));
 }
 
 // The same for a grouped product: only the rows that the tile list covers are finished (other rows of `out` belong
@@ -645,6 +655,10 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
                       cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
+  if (swiglu < 0 || swiglu > NV_EPI_SILU) return NV_ERR_BAD_SIZE;
+  const int act = swiglu >= 2 ? swiglu : 0;          // (see common.cuh: what the `swiglu` argument may say)
+  swiglu = swiglu == NV_EPI_SWIGLU;
+  if (act && tile_expert) return NV_ERR_UNSUPPORTED; // a unary activation: dense products only
   if (n_tile < 16 || n_tile > 256 || (n_tile & (n_tile - 1))) return NV_ERR_BAD_SIZE;
   if (M_tok <= 0 || N <= 0) return NV_OK;
   const bool grouped = tile_expert != nullptr;
@@ -667,7 +681,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.k_steps_total = (K + BLOCK_K - 1) / BLOCK_K;
   a.splits = splits < 1 ? 1 : splits;
   a.k_steps_per_split = (a.k_steps_total + a.splits - 1) / a.splits;
-  a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0;
+  a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0; a.act = act;
   a.early = early ? 1 : 0;
   a.x_box = x_box;
   a.x_sub = x_sub; a.x_mod = x_mod;
@@ -763,7 +777,8 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
     } else {
       const long long outputs = (long long)a.M_out * N;
       NV_RETURN_IF(launch_dep(tc_gemm_finish_kernel, dim3((unsigned)((outputs + 255) / 256)), dim3(256), 0, stream,
-                              (const float*)scratch, a.splits, a.M_out, N, a.swiglu, bias, bias_dt, out, out_dt, ldo));
+                              (const float*)scratch, a.splits, a.M_out, N, a.act ? a.act : a.swiglu, bias, bias_dt, out,
+                              out_dt, ldo));
     }
   }
   NV_RETURN_LAST();

@@ -16,9 +16,10 @@ SKINNY_ROWS = ops.SKINNY_MAX_ROWS
 SKINNY_MAX_BYTES = 128 << 20
 
 
-def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None, out=None):
+def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None, out=None, act=None):
     """``out = a[a_rows] @ w.T (+ bias)``; with ``swiglu`` w is [2N, K] (gate rows, then up rows)
-    and ``out = silu(a @ gate.T) * (a @ up.T)``."""
+    and ``out = silu(a @ gate.T) * (a @ up.T)``; with ``act`` (gelu_erf, gelu_tanh, silu) every value of the
+    result passes that function in the product's epilogue, on the float32 sum."""
     rows_w = w.shape[0]
     N = rows_w // 2 if swiglu else rows_w
     if M is None:
@@ -32,12 +33,12 @@ def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None
         # a handful of rows: the product is a stream of w, and the kernel without tiles starts it soonest
         if a_rows is not None:
             a = ops.permute_rows(a, a_rows, M)
-        ops.skinny_gemm(a, w, out, bias=bias, swiglu=swiglu, rows=M, err=ctx.err)
+        ops.skinny_gemm(a, w, out, bias=bias, swiglu=swiglu, rows=M, err=ctx.err, act=act)
         return out
     if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu):
-        ops.gemm_fast(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu, M=M, err=ctx.err)
+        ops.gemm_fast(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu, M=M, err=ctx.err, act=act)
     else:
-        ops.gemm_plain(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu, M=M)
+        ops.gemm_plain(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu, M=M, act=act)
     return out
 
 

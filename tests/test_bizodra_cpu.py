@@ -53,6 +53,22 @@ def test_config_errors_name_the_key(path, value, word):
         BizodraConfig.from_dict(cfg)
 
 
+def test_layer_types_with_numeric_suffixes_name_the_same_kinds():
+    from nano_vllm_cpp_b200.config import BizodraConfig, ConfigError
+    from nano_vllm_cpp_b200.config.bizodra_config import MatrixLstmConfig, ParallelConfig
+    cfg = copy.deepcopy(CONFIGS["Q"])
+    cfg["layers"][0]["type"], cfg["layers"][1]["type"], cfg["layers"][2]["type"] = "mlstm_3", "parallel", "parallel_2"
+    typed = BizodraConfig.from_dict(cfg)
+    assert [type(L.mixer) for L in typed.layers] == [MatrixLstmConfig, ParallelConfig, ParallelConfig]
+    for bad in ("mlstm_", "_2", "mlstm_x", "parallel2"):
+        cfg["layers"][0]["type"] = bad
+        with pytest.raises(ConfigError, match="type"):
+            BizodraConfig.from_dict(cfg)
+    del cfg["layers"][1]["mixer"]["left"]["rot"]            # without 'rot' nothing is turned
+    cfg["layers"][0]["type"] = "mlstm"
+    assert BizodraConfig.from_dict(cfg).layers[1].mixer.left.rot.dims == 0
+
+
 def test_what_the_mixers_keep_per_request():
     from nano_vllm_cpp_b200.parts import KVCacheSpec, StateCacheSpec, CompositeCacheSpec
     _, _, model = build(CONFIGS["P"])

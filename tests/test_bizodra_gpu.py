@@ -323,6 +323,33 @@ def test_layer_pieces_alone(dtype):
     close(xs, stream + pb.rms(mixed, eps) * (1 + W["l0.norm1"]), 1e-5, "stream after two mixed branches")
 
 
+@pytest.mark.parametrize("act", ["gelu_erf", "gelu_tanh", "silu"])
+def test_activation_in_the_products_epilogues(act):
+    """Every product kernel applies a unary activation to its float32 sums after the bias: the one that streams the
+    weights for a handful of rows, the tensor-core one (whole, with two weight tiles per block, and with K split
+    and a finishing kernel), and the plain one in float32."""
+    from nano_vllm_cpp_b200.csrc import ops
+    fn = {"gelu_erf": pb.gelu_erf, "gelu_tanh": pb.gelu_tanh, "silu": pb.silu}[act]
+    g = torch.Generator().manual_seed(61)
+    K, N = 256, 328
+    w = (torch.randn(N, K, generator=g) / 16).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g)
+    for M, kind in ((5, "skinny"), (300, "fast"), (2048, "fast"), (300, "split"), (37, "plain")):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        want = fn(x.double() @ w.double().T + bias.double())
+        if kind == "plain":
+            out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+            ops.gemm_plain(x.float().to(DEV), w.float().to(DEV), out, bias=bias.to(DEV), act=act)
+            close(out, want, 1e-5, f"{act} plain")
+            continue
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        if kind == "skinny":
+            ops.skinny_gemm(x.to(DEV), w.to(DEV), out, bias=bias.to(DEV), act=act)
+        else:
+            ops.gemm_fast(x.to(DEV), w.to(DEV), out, bias=bias.to(DEV), act=act, splits=3 if kind == "split" else None)
+        close(out, want, 2 ** -7, f"{act} {kind} M={M}")
+
+
 # ------------------------------------------------------------------------------- whole models through the engine
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["P", "Q"])
@@ -442,3 +469,25 @@ def test_greedy_generation_through_the_engine(dtype, models):
                 assert lead <= bound, f"token {k} of a prompt of {len(p)}: {tok}, plain takes {best} with a lead of {lead:.3g}"
                 break
             seq.append(tok)
+
+
+def test_command_line_serves_the_design(models, tmp_path, capsys):
+    """``nanovllm <folder> --tokens ...`` and ``nanovllm --config <json>`` (random weights) run this design as they
+    run the other; the greedy tokens from the folder are the plain implementation's."""
+    import json
+    from nano_vllm_cpp_b200 import cli
+    name = "Q"
+    cfg, W, folder = models[name]
+    prompt = ids_for(name, 7, salt=30)
+    rc = cli.main([folder, "--tokens", ",".join(map(str, prompt)), "--max-tokens", "6", "--temperature", "0",
+                   "--dtype", "float32", "--max-model-len", "64", "--num-kv-blocks", "8", "--ignore-eos"])
+    out = capsys.readouterr().out
+    assert rc == 0, out
+    toks = [int(t) for t in out.strip().splitlines()[-1].split(":")[1].split()]
+    assert toks == pb.greedy_generate(cfg, W, prompt, 6)
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(CONFIGS["P"]))
+    rc = cli.main(["--config", str(path), "--seed", "4", "--tokens", "5,6,7", "--max-tokens", "4", "--temperature", "0",
+                   "--max-model-len", "64", "--num-kv-blocks", "8", "--ignore-eos"])
+    out = capsys.readouterr().out
+    assert rc == 0 and len(out.strip().splitlines()[-1].split(":")[1].split()) == 4
