@@ -293,6 +293,12 @@ def design_bench(args) -> int:
             ms = timed(prefill_many, 3)
             row["prefill_together"] = {"prompts": len(many), "tokens": T * len(many), "ms": round(ms, 3),
                                        "tokens_per_s": round(T * len(many) / ms * 1e3, 1)}
+            graphs, runner.cuda_graphs = runner.cuda_graphs, False
+            with ops.KernelTimes() as kt:
+                prefill_many()
+            row["prefill_together"]["kernels"] = [{"name": r["name"], "calls": r["calls"], "ms": round(r["ms"], 3)}
+                                                  for r in kt.summary()[:6]]
+            runner.cuda_graphs = graphs
             # the prompt's kernels one by one (outside graphs, an event between any two)
             graphs, runner.cuda_graphs = runner.cuda_graphs, False
             with ops.KernelTimes() as kt:

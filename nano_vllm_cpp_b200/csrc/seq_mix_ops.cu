@@ -538,15 +538,16 @@ __global__ void __launch_bounds__(ATTG_THREADS) paged_attention_general_kernel(
 // A column of the head's matrix (its dk rows) stays in one thread's registers while the entry's rows run: the
 // columns of either recurrence never meet, so a row costs one barrier (for q and k of the row, staged in shared
 // memory through a ring of asynchronous copies) and a few exchanges between the neighbouring lanes that hold the
-// column's rows, sixteen each.  The kernel waits on shared memory and on its own short chains more than it issues,
-// so it wants many warps on a multiprocessor: a block is two warps with eight to thirty-two columns; blocks along z share a head's columns, so a single sequence fills more multiprocessors and a
+// column's rows, thirty-two each, four at a time in turn (so that their reads of q and k in shared memory lie side
+// by side: with a lane's rows in one stretch every such read was a four-way bank conflict, and a step of eight
+// prompts took 5.4 instead of 1.6 ms).  A block is two warps with sixteen to sixty-four columns; blocks along z share a head's columns, so a single sequence fills more multiprocessors and a
 // decode step's read of the states is spread over them.  The matrix LSTM's normaliser is one more column (whose
 // value is 1), and its product with q one more output.  What needs a whole head, the division by the normaliser,
 // the head's RMS norm and the output gate, follows in head_finish_kernel, a row and head per warp.
 // raw: [T, H, RW] float32, RW = dv (+ 2 for the matrix LSTM: n . q and the running maximum m behind the dv sums).
 constexpr int COL_THREADS = 64;
-constexpr int COL_ROWS = 16;                           // rows of a column that one thread holds: DK / 16 lanes share a column
-constexpr int COL_MAX_COLS = COL_THREADS / 2;          // columns of a block at most (DK = 32)
+constexpr int COL_ROWS = 32;                           // rows of a column that one thread holds: DK / 32 lanes share a column
+
 
 struct ColArgs {
   const int* cu_rows;
@@ -572,6 +573,7 @@ struct ColArgs {
   float cap, q_scale;
   float* raw;
   int RW, H, dk, dv;
+  int vec16;                // q and k can be copied sixteen bytes at a time (set by the launcher from the addresses)
 };
 
 // The gates of a row and head, ready for the recurrence: the matrix LSTM's capped log gates (i, f), or the delta
@@ -606,6 +608,10 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
                : "memory");
 }
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -618,7 +624,7 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
   // with one row ahead every row waited for its loads' way through the memory system.
   __shared__ __align__(16) float qs[COL_RING][DK];
   __shared__ __align__(16) float ks[COL_RING][DK];
-  constexpr int COL_RSPLIT = DK / COL_ROWS;          // lanes that share a column (2, 4 or 8)
+  constexpr int COL_RSPLIT = DK / COL_ROWS;          // lanes that share a column (1, 2 or 4)
   constexpr int COL_COLS = COL_THREADS / COL_RSPLIT; // columns of a block
   __shared__ float vs[COL_RING][COL_COLS];
   __shared__ float gs[COL_RING][2];
@@ -630,7 +636,9 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
   const int half = tid % COL_RSPLIT;                 // neighbouring lanes share a column, each a part of its rows
   const int cl = tid / COL_RSPLIT;                   // the column's place in the block
   const int c = blockIdx.z * COL_COLS + cl;
-  const int rbase = half * DKH;
+  // The lanes of a column take its rows four at a time in turn (lane `half` holds rows 4 (half + RSPLIT j) .. + 3,
+  // j = 0, 1, ...): their 16-byte reads of q and k in shared memory then lie side by side, without bank conflicts.
+  auto row_of = [&](int r) { return 4 * (half + COL_RSPLIT * (r / 4)) + (r % 4); };
   const int ncols = MODE == 0 ? dv + 1 : dv;
   const bool active = c < ncols;
   const bool is_n = MODE == 0 && c == dv;
@@ -644,7 +652,7 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
   }
   float Sreg[DKH];
 #pragma unroll
-  for (int r = 0; r < DKH; ++r) Sreg[r] = (active && rbase + r < dk) ? colp[(size_t)(rbase + r) * cstride] : 0.f;
+  for (int r = 0; r < DKH; ++r) Sreg[r] = (active && row_of(r) < dk) ? colp[(size_t)row_of(r) * cstride] : 0.f;
   float m = 0.f, rate = 0.f, dtb = 0.f;
   if (MODE == 0) m = a.m[(size_t)slot * a.m_stride + h];
   else { rate = expf(a.A_log[h]); dtb = a.dt_bias[h]; }
@@ -655,33 +663,52 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
     for (int i = 0; i < COL_RING; ++i) vs[i][cl] = 1.f;
   const float* gates = (const float*)a.gates;
   const bool has_v = active && !is_n && half == 0;
+  // where this thread's copies of the next row to fetch come from; they move on by a row per fetch.  With
+  // a.vec16 (every q and k head starts on a 16-byte boundary) a thread copies four floats at once: threads
+  // 0 .. DK/4 - 1 the row's q, the next DK/4 its k; else one float at a time.
+  constexpr int Q4 = DK / 4;                         // 16-byte pieces of a head's q (or k)
+  const bool k_side = tid >= Q4;
+  const int piece = k_side ? tid - Q4 : tid;         // (with vec16)
+  const float* src_q = a.qk + (size_t)row0 * a.qk_ld + a.q0 + gh * dk + tid;
+  const float* src_k = a.qk + (size_t)row0 * a.qk_ld + a.k0 + gh * dk + tid;
+  const float* src_16 = a.qk + (size_t)row0 * a.qk_ld + (k_side ? a.k0 : a.q0) + gh * dk + 4 * piece;
+  const bool does_16 = a.vec16 && tid < 2 * Q4 && 4 * piece < dk;
+  const float* src_v = a.vsrc + (size_t)row0 * a.v_ld + a.v0 + h * dv + (has_v ? c : 0);
+  const float* src_g = gates + (size_t)row0 * a.gates_ld + (tid == 1 ? a.gb0 : a.ga0) + (PRE ? 2 * h : h);
+  int fetch_slot = 0;
   auto fetch = [&](int t) {
     if (t < row1) {
-      const int b = (t - row0) % COL_RING;
-      const float* x = a.qk + (size_t)t * a.qk_ld;
+      const int b = fetch_slot;
+      if (a.vec16) {
+        if (does_16) cp_async16((k_side ? ks[b] : qs[b]) + 4 * piece, src_16);
+      } else {
 #pragma unroll
-      for (int i = 0; i < PER; ++i) {
-        const int r = tid + i * COL_THREADS;
-        if (r < dk && r < DK) {
-          cp_async4(&qs[b][r], x + a.q0 + gh * dk + r);
-          cp_async4(&ks[b][r], x + a.k0 + gh * dk + r);
+        for (int i = 0; i < PER; ++i) {
+          const int r = tid + i * COL_THREADS;
+          if (r < dk && r < DK) {
+            cp_async4(&qs[b][r], src_q + i * COL_THREADS);
+            cp_async4(&ks[b][r], src_k + i * COL_THREADS);
+          }
         }
       }
-      if (has_v) cp_async4(&vs[b][cl], a.vsrc + (size_t)t * a.v_ld + a.v0 + h * dv + c);
-      if (tid < 2) cp_async4(&gs[b][tid], gates + (size_t)t * a.gates_ld + (tid ? a.gb0 : a.ga0) + (PRE ? 2 * h : h));
+      if (has_v) cp_async4(&vs[b][cl], src_v);
+      if (tid < 2) cp_async4(&gs[b][tid], src_g);
+      src_q += a.qk_ld; src_k += a.qk_ld; src_16 += a.qk_ld; src_v += a.v_ld; src_g += a.gates_ld;
+      fetch_slot = (fetch_slot + 1) % COL_RING;
     }
     cp_async_commit();                               // (a group per row, also an empty one: the count below relies on it)
   };
   for (int j = 0; j < COL_RING - 1; ++j) fetch(row0 + j);
-  for (int t = row0; t < row1; ++t) {
+  float* out = a.raw + ((size_t)row0 * a.H + h) * a.RW;
+  const size_t out_step = (size_t)a.H * a.RW;
+  for (int t = row0; t < row1; ++t, out += out_step) {
     const int b = (t - row0) % COL_RING;
     cp_async_wait<COL_RING - 2>();                   // this thread's copies of row t have landed ...
     __syncthreads();                                 // ... and everyone's; and everyone is done with row t - 1,
     fetch(t + COL_RING - 1);                         // whose place in the ring the new row takes
     const float v = vs[b][cl], ga = gs[b][0], gb = gs[b][1];
-    const float4* q4 = reinterpret_cast<const float4*>(qs[b] + rbase);
-    const float4* k4 = reinterpret_cast<const float4*>(ks[b] + rbase);
-    float* out = a.raw + ((size_t)t * a.H + h) * a.RW;
+    const float4* q4 = reinterpret_cast<const float4*>(qs[b]) + half;      // piece j of this lane: q4[RSPLIT * j]
+    const float4* k4 = reinterpret_cast<const float4*>(ks[b]) + half;
     if (MODE == 0) {
       float ig = ga, fg = gb;
       if (!PRE) scan_gates(0, ga, gb, a.cap, 0.f, 0.f, ig, fg);
@@ -691,7 +718,7 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;          // four chains; added up in a fixed order
 #pragma unroll
       for (int r4 = 0; r4 < DKH / 4; ++r4) {
-        const float4 qq = q4[r4], kk = k4[r4];
+        const float4 qq = q4[COL_RSPLIT * r4], kk = k4[COL_RSPLIT * r4];
         float s;
         s = fmaf(fa, Sreg[4 * r4 + 0], kk.x * bv); Sreg[4 * r4 + 0] = s; a0 = fmaf(s, qq.x, a0);
         s = fmaf(fa, Sreg[4 * r4 + 1], kk.y * bv); Sreg[4 * r4 + 1] = s; a1 = fmaf(s, qq.y, a1);
@@ -709,7 +736,7 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
       float ak = 0.f, aq = 0.f, kq = 0.f, ak1 = 0.f, aq1 = 0.f, kq1 = 0.f;     // two chains each
 #pragma unroll
       for (int r4 = 0; r4 < DKH / 4; ++r4) {
-        const float4 qq = q4[r4], kk = k4[r4];
+        const float4 qq = q4[COL_RSPLIT * r4], kk = k4[COL_RSPLIT * r4];
         ak = fmaf(Sreg[4 * r4 + 0], kk.x, ak); aq = fmaf(Sreg[4 * r4 + 0], qq.x, aq); kq = fmaf(kk.x, qq.x, kq);
         ak1 = fmaf(Sreg[4 * r4 + 1], kk.y, ak1); aq1 = fmaf(Sreg[4 * r4 + 1], qq.y, aq1); kq1 = fmaf(kk.y, qq.y, kq1);
         ak = fmaf(Sreg[4 * r4 + 2], kk.z, ak); aq = fmaf(Sreg[4 * r4 + 2], qq.z, aq); kq = fmaf(kk.z, qq.z, kq);
@@ -726,7 +753,7 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
       if (active && half == 0) out[c] = fmaf(kq, u, g * aq) * a.q_scale;
 #pragma unroll
       for (int r4 = 0; r4 < DKH / 4; ++r4) {
-        const float4 kk = k4[r4];
+        const float4 kk = k4[COL_RSPLIT * r4];
         Sreg[4 * r4 + 0] = fmaf(g, Sreg[4 * r4 + 0], kk.x * u);
         Sreg[4 * r4 + 1] = fmaf(g, Sreg[4 * r4 + 1], kk.y * u);
         Sreg[4 * r4 + 2] = fmaf(g, Sreg[4 * r4 + 2], kk.z * u);
@@ -738,7 +765,7 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
   if (active) {
 #pragma unroll
     for (int r = 0; r < DKH; ++r)
-      if (rbase + r < dk) colp[(size_t)(rbase + r) * cstride] = Sreg[r];
+      if (row_of(r) < dk) colp[(size_t)row_of(r) * cstride] = Sreg[r];
   }
   if (MODE == 0 && blockIdx.z == 0 && tid == 0) a.m[(size_t)slot * a.m_stride + h] = m;
 }
@@ -787,6 +814,8 @@ int launch_col_scan_p(const ColArgs& a, int S, cudaStream_t s) {
 
 template <int MODE>
 int launch_col_scan(ColArgs a, int S, int T, float* gate_buf, cudaStream_t s) {
+  // sixteen-byte copies: every row's q and k heads start on 16-byte boundaries and a head is whole pieces
+  a.vec16 = (((uintptr_t)a.qk & 15) == 0 && a.qk_ld % 4 == 0 && a.q0 % 4 == 0 && a.k0 % 4 == 0 && a.dk % 4 == 0) ? 1 : 0;
   if (T > SCAN_GATES_APART_ROWS && gate_buf) {
     const long long n = (long long)T * a.H;
     scan_gates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float*)a.gates, a.gates_ld, a.ga0, a.gb0, a.H,
