@@ -324,6 +324,20 @@ def test_layer_pieces_alone(dtype):
 
 
 @pytest.mark.parametrize("act", ["gelu_erf", "gelu_tanh", "silu"])
+def test_activation_pass(act):
+    """The activation as a pass of its own: four values per thread where the size allows, else one."""
+    from nano_vllm_cpp_b200.csrc import ops
+    fn = {"gelu_erf": pb.gelu_erf, "gelu_tanh": pb.gelu_tanh, "silu": pb.silu}[act]
+    g = torch.Generator().manual_seed(60)
+    for shape in ((7, 13), (64, 256), (3, 20)):
+        z = 3 * torch.randn(shape, generator=g)
+        for out_dtype, rel in ((torch.bfloat16, 2 ** -7), (torch.float32, 1e-6)):
+            out = torch.empty(shape, dtype=out_dtype, device=DEV)
+            ops.activation(z.to(DEV), out, act)
+            close(out, fn(z.double()), rel, f"{act} {shape} {out_dtype}")
+
+
+@pytest.mark.parametrize("act", ["gelu_erf", "gelu_tanh", "silu"])
 def test_activation_in_the_products_epilogues(act):
     """Every product kernel applies a unary activation to its float32 sums after the bias: the one that streams the
     weights for a handful of rows, the tensor-core one (whole, with two weight tiles per block, and with K split
