@@ -5,33 +5,49 @@
 
 #include "common.cuh"
 
+// How a row's router logits become choices and weights.  mode 0: p = softmax(logits), the K largest p are chosen
+// and weigh p (or p / their sum).  mode 1: s = sigmoid(logit) in float32; the K largest s + bias[e] are chosen
+// (bias may be nullptr) and weigh s, without the bias.  Either way the weights are multiplied by `scale`.
+struct RouteRule {
+  int mode;
+  const float* bias;
+  float scale;
+};
+
 // One warp routes one row: p = softmax(logits) over all E in double, then K rounds of "largest
 // remaining, lowest index on a tie", optional renormalisation of the K weights in double
-// (src/hip_ops.hip:813-841).  `pr` is E doubles of scratch for this warp.  With C > 0 the row also
-// gets C "always on" experts E .. E+C-1 with weight sigmoid(gate_logit): the chunks of a shared
-// expert that is computed as C more experts (src/model.cpp:803-811 computes it separately).
-// idx and score rows are K + C wide.
+// (src/hip_ops.hip:813-841); or the sigmoid rule of RouteRule.  `pr` is E doubles of scratch for this warp.
+// With C > 0 the row also gets C "always on" experts E .. E+C-1 with weight sigmoid(gate_logit), or 1 without a
+// gate: the chunks of a shared expert that is computed as C more experts (src/model.cpp:803-811 computes it
+// separately).  idx and score rows are K + C wide.
 __device__ __forceinline__ void route_row(const float* __restrict__ r, int E, int K, int renorm, double* pr,
                                           int lane, int* __restrict__ idx_row, float* __restrict__ score_row,
-                                          int C, const float* gate_logit) {
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, r[e]);
-  mx = warp_max(mx);
-  double s = 0.0;
-  for (int e = lane; e < E; e += 32) {
-    double v = exp((double)r[e] - (double)mx);
-    pr[e] = v;
-    s += v;
-  }
+                                          int C, const float* gate_logit, RouteRule rule) {
+  if (rule.mode == 1) {
+    for (int e = lane; e < E; e += 32) {
+      const float sg = 1.f / (1.f + expf(-r[e]));
+      pr[e] = (double)(rule.bias ? sg + rule.bias[e] : sg);
+    }
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, r[e]);
+    mx = warp_max(mx);
+    double s = 0.0;
+    for (int e = lane; e < E; e += 32) {
+      double v = exp((double)r[e] - (double)mx);
+      pr[e] = v;
+      s += v;
+    }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  __syncwarp();
-  for (int e = lane; e < E; e += 32) pr[e] /= s;
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) pr[e] /= s;
+  }
   __syncwarp();
   double wsum = 0.0;
   double mine = 0.0;  // lane k keeps the k-th weight (K <= 32)
   for (int k = 0; k < K; ++k) {
-    double best = -1.0;
+    double best = -1.0e300;                 // (a choice score may be negative; a taken expert is -infinity)
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
       double v = pr[e];
@@ -43,15 +59,19 @@ __device__ __forceinline__ void route_row(const float* __restrict__ r, int E, in
       int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
     }
+    if (rule.mode == 1) best = (double)(1.f / (1.f + expf(-r[bi])));     // the weight is the score without the bias
     if (lane == k) { mine = best; idx_row[k] = bi; }
     wsum += best;
-    if (lane == 0) pr[bi] = -2.0;
+    if (lane == 0) pr[bi] = -INFINITY;
     __syncwarp();
   }
-  if (lane < K) score_row[lane] = (float)(renorm ? mine / wsum : mine);
+  if (lane < K) {
+    const float wk = (float)(renorm ? mine / wsum : mine);
+    score_row[lane] = rule.scale == 1.f ? wk : wk * rule.scale;
+  }
   if (lane < C) {
     idx_row[K + lane] = E + lane;
-    score_row[K + lane] = 1.f / (1.f + expf(-gate_logit[0]));
+    score_row[K + lane] = gate_logit ? 1.f / (1.f + expf(-gate_logit[0])) : 1.f;
   }
 }
 

@@ -253,13 +253,14 @@ def random_fill(out, key: int, mean: float, std: float) -> None:
                                 mean, std, _stream()), "random_fill")
 
 
-def embedding(ids, table, out, err: ErrorFlag, feed=None) -> None:
-    """``feed``: int32 tokens that negative ids point into (id ``-(r + 1)`` reads ``feed[r]``)."""
+def embedding(ids, table, out, err: ErrorFlag, feed=None, copies: int = 1) -> None:
+    """``feed``: int32 tokens that negative ids point into (id ``-(r + 1)`` reads ``feed[r]``).  ``copies``: a row of
+    ``out`` [T, copies * H] holds the token's row that many times, side by side."""
     _cuda_contig(ids, table, out, feed)
     _i32(ids, feed)
     T, (V, H) = ids.numel(), table.shape
-    _need(out.dtype == torch.float32 and out.shape == (T, H), "embedding: out must be float32 [T, H]")
-    _check(lib().nv_embedding(_p(ids), _p(feed), _p(table), dt(table), _p(out), T, H, V,
+    _need(out.dtype == torch.float32 and out.shape == (T, copies * H), "embedding: out must be float32 [T, copies * H]")
+    _check(lib().nv_embedding(_p(ids), _p(feed), _p(table), dt(table), _p(out), T, H, V, copies,
                               _p(err.t), _stream()), "embedding")
 
 
@@ -498,19 +499,37 @@ def paged_attention_plain(qkv, k_cache, v_cache, block_table, row_entry, positio
                                           _stream()), "paged_attention_plain")
 
 
-def router_topk(logits, K: int, renorm: bool, idx, score, C: int = 0, gate_logit=None) -> None:
+ROUTE_SCORES = {"softmax": 0, "sigmoid": 1}
+
+
+def _route_rule(rule, E: int):
+    """``rule`` = None (softmax, no bias, weights as they are) or (score kind, choice bias [E] float32 or None,
+    weight scale): what the routing kernels take as their last three arguments."""
+    if rule is None:
+        return 0, None, 1.0
+    kind, bias, scale = rule
+    _need(kind in ROUTE_SCORES, f"router: the score is one of {sorted(ROUTE_SCORES)}")
+    _need(bias is None or (kind == "sigmoid" and bias.is_cuda and bias.dtype == torch.float32 and bias.is_contiguous()
+                           and bias.numel() == E), "router: the choice bias is float32 [E], with sigmoid scores")
+    return ROUTE_SCORES[kind], bias, float(scale)
+
+
+def router_topk(logits, K: int, renorm: bool, idx, score, C: int = 0, gate_logit=None, rule=None) -> None:
     """``logits`` may be a column slice of a wider float32 matrix (rows ``stride(0)`` apart).  With ``C`` the
-    rows of ``idx``/``score`` are K + C wide: C always-on experts E..E+C-1 weighted sigmoid(gate_logit)."""
+    rows of ``idx``/``score`` are K + C wide: C always-on experts E..E+C-1 weighted sigmoid(gate_logit), or 1
+    without gate logits.  ``rule``: see ``_route_rule``."""
     _cuda_contig(idx, score)
     _need(logits.is_cuda and logits.stride(1) == 1, "router: logits rows must be dense")
     T, E = logits.shape
     _need(logits.dtype == torch.float32 and score.dtype == torch.float32, "router: float32 logits and scores")
     _i32(idx)
     _need(idx.shape == (T, K + C) and score.shape == (T, K + C), "router: output shapes")
-    _need(C == 0 or (gate_logit is not None and gate_logit.dtype == torch.float32), "router: gate logits")
+    _need(gate_logit is None or gate_logit.dtype == torch.float32, "router: gate logits")
+    mode, bias, wscale = _route_rule(rule, E)
     _check(lib().nv_router_topk(_p(logits), logits.stride(0), T, E, K,
                                 (1 if renorm else 0), _p(idx), _p(score), C, _p(gate_logit),
-                                (gate_logit.stride(0) if gate_logit is not None else 0), _stream()),
+                                (gate_logit.stride(0) if gate_logit is not None else 0), mode, _p(bias), wscale,
+                                _stream()),
            "router_topk")
 
 
@@ -589,7 +608,7 @@ def moe_route_small_usable(T: int, E: int, K: int, C: int, H: int) -> bool:
 
 
 def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score, al: "MoeAlignment", err, x=None,
-                    static: bool = False, zero=None):
+                    static: bool = False, zero=None, rule=None):
     """Top-k, expert permutation and (with ``x``, bfloat16 rows) the expert-sorted copy of x, in one launch.
     Returns the sorted copy or None.  ``static``: the C always-on experts' pairs sit in row order at the end of
     the permutation and get no tiles (``static_tiles`` lists them; they can then run before the routing).
@@ -604,13 +623,15 @@ def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score
         _need(x.dtype == torch.bfloat16 and x.is_contiguous(), "route: bfloat16 rows")
         H = x.shape[1]
         xs = torch.empty((T * KT, H), dtype=x.dtype, device=x.device)
+    mode, bias, wscale = _route_rule(rule, E)
     _check(lib().nv_moe_route_small(_p(logits), logits.stride(0), T, E, K,
                                     (1 if renorm else 0), C, _p(gate_logit),
                                     (gate_logit.stride(0) if gate_logit is not None else 0), _p(idx),
                                     _p(score), al.tile_m, _p(al.counts), _p(al.offsets), _p(al.sorted_token),
                                     _p(al.pair_pos), _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows),
                                     _p(al.num_tiles), _p(err.t), _p(x), _p(xs), H, (C if static else 0),
-                                    _p(zero), (zero.numel() if zero is not None else 0), _stream()), "moe_route_small")
+                                    _p(zero), (zero.numel() if zero is not None else 0), mode, _p(bias), wscale,
+                                    _stream()), "moe_route_small")
     return xs
 
 
@@ -901,6 +922,64 @@ def paged_attention_general(q, k_cache, v_cache, block_table, row_entry, positio
 
 # ----------------------------------------------------------------------------- fast products
 _num_sms = None
+
+
+def stream_mix_norm(x, streams: int, *, branch=None, mix=None, carry=None, write=None, read=None, norm=None,
+                    out=None, out32=None) -> None:
+    """The copies of the residual stream ``x`` [T, streams * H] (float32, copy after copy inside a row), in one launch:
+
+    1. with a pending sublayer output y (``branch`` [T, H] float32, or ``mix`` = (rows, index, weight, dense, None):
+       ``y = dense + sum_r weight[:, r] * rows[index[:, r]]``) every copy d becomes
+       ``sum_c carry[c, d] * x_c + write[d] * y`` (``carry`` [streams, streams] indexed [from, to], ``write``
+       [streams]); with one copy and neither tensor ``x += y``;
+    2. ``u = sum_d read[d] * x_d`` (``read`` None: the plain sum of the copies);
+    3. ``norm`` = (alpha [1], gain [H], shift [H]), all float32: ``tanh(alpha * u) * gain + shift``; None: u itself;
+    4. the result goes to ``out`` (float32 or bfloat16) and / or ``out32``; with neither, only step 1 is done."""
+    _need(x.dtype == torch.float32 and x.is_cuda and x.is_contiguous() and x.dim() == 2 and x.shape[1] % streams == 0,
+          "stream_mix_norm: the copies are float32 [T, streams * H]")
+    T, H = x.shape[0], x.shape[1] // streams
+    rows = index = weight = dense = None
+    R = 0
+    if mix is not None:
+        _need(branch is None, "stream_mix_norm: one form of the pending output at a time")
+        rows, index, weight, dense, gate = mix
+        _need(gate is None, "stream_mix_norm: a gated dense term is not taken")
+        R = index.shape[1]
+        _need(R <= STREAM_MAX_MIX, f"stream_mix_norm: at most {STREAM_MAX_MIX} rows are mixed per token")
+        _need(rows.dtype == torch.float32 and rows.shape[1] == H and rows.is_contiguous() and index.dtype == torch.int32
+              and weight.dtype == torch.float32 and index.shape == (T, R) and weight.shape == (T, R)
+              and index.is_contiguous() and weight.is_contiguous(), "stream_mix_norm: mix shapes")
+    for t_ in (branch, dense, out32):
+        _need(t_ is None or (t_.dtype == torch.float32 and t_.shape == (T, H) and t_.is_contiguous()),
+              "stream_mix_norm: float32 [T, H] rows")
+    _need(out is None or (out.shape == (T, H) and out.is_contiguous()), "stream_mix_norm: out is [T, H]")
+    _need((carry is None) == (write is None), "stream_mix_norm: carry and write come together")
+    if carry is not None:
+        _need(carry.dtype == torch.float32 and carry.shape == (streams, streams) and carry.is_contiguous()
+              and write.dtype == torch.float32 and write.numel() == streams, "stream_mix_norm: carry / write shapes")
+    _need(read is None or (read.dtype == torch.float32 and read.numel() == streams), "stream_mix_norm: read shape")
+    alpha = gain = shift = None
+    if norm is not None:
+        alpha, gain, shift = norm
+        _f32(alpha, gain, shift)
+        _need(alpha.numel() == 1 and gain.numel() == H and shift.numel() == H, "stream_mix_norm: norm shapes")
+    if H % 4 == 0:
+        for t_ in (x, branch, rows, dense, out, out32, gain, shift):
+            _need(t_ is None or t_.data_ptr() % 16 == 0, "stream_mix_norm: rows must start on 16-byte boundaries")
+    _check(lib().nv_stream_mix_norm(_p(x), T, streams, H, _p(branch), _p(rows), _p(index), _p(weight), R, _p(dense),
+                                    _p(carry), _p(write), _p(read), (0 if norm is None else 1), _p(alpha), _p(gain),
+                                    _p(shift), _p(out), (dt(out) if out is not None else 0), _p(out32), _stream()),
+           "stream_mix_norm", nbytes=4.0 * T * H * (2 * streams + 2))
+
+
+STREAM_MAX_STREAMS = 8
+STREAM_MAX_MIX = 64
+
+
+def scale_softcap(z, scale: float, cap: float) -> None:
+    """``z = cap * tanh(scale * z / cap)`` in place (``cap`` <= 0: ``scale * z``); float32."""
+    _need(z.dtype == torch.float32 and z.is_cuda and z.is_contiguous(), "scale_softcap: float32 values")
+    _check(lib().nv_scale_softcap(_p(z), z.numel(), float(scale), float(cap), _stream()), "scale_softcap")
 
 
 def num_sms() -> int:

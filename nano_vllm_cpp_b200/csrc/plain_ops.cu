@@ -17,7 +17,7 @@ namespace {
 // seen the tokens of the step before.
 __global__ void embedding_kernel(const int* __restrict__ ids, const void* __restrict__ table, int dt,
                                  float* __restrict__ out, int H, int V, int* __restrict__ err,
-                                 const int* __restrict__ feed) {
+                                 const int* __restrict__ feed, int copies) {
   grid_dep_wait();
   grid_dep_launch();
   int t = blockIdx.x;
@@ -27,7 +27,12 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const void* __rest
     if (threadIdx.x == 0) atomicExch(err, 1 + t);
     id = 0;
   }
-  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)t * H + i] = ld_dt(table, dt, (size_t)id * H + i);
+  // `copies` > 1: a row of `out` holds that many copies of the table's row side by side (a model that keeps
+  // several copies of its residual stream starts them all from the embedding)
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = ld_dt(table, dt, (size_t)id * H + i);
+    for (int c = 0; c < copies; ++c) out[((size_t)t * copies + c) * H + i] = v;
+  }
 }
 
 // ---------------------------------------------------------- residual add + RMSNorm
@@ -404,13 +409,13 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_plain_kernel(
 // (the work is in moe_route.cuh)
 __global__ void router_topk_kernel(const float* __restrict__ logits, long long ld, int T, int E, int K, int renorm,
                                    int* __restrict__ idx, float* __restrict__ score, int C,
-                                   const float* __restrict__ gate_logit, long long gate_ld) {
+                                   const float* __restrict__ gate_logit, long long gate_ld, RouteRule rule) {
   extern __shared__ double sm[];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int t = blockIdx.x * (blockDim.x / 32) + warp;
   if (t >= T) return;
   route_row(logits + (size_t)t * ld, E, K, renorm, sm + (size_t)warp * E, lane, idx + (size_t)t * (K + C),
-            score + (size_t)t * (K + C), C, C ? gate_logit + (size_t)t * gate_ld : nullptr);
+            score + (size_t)t * (K + C), C, (C && gate_logit) ? gate_logit + (size_t)t * gate_ld : nullptr, rule);
 }
 
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ idx, int TK, int K, int E,
@@ -554,10 +559,12 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 NV_API const char* nv_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
 
 NV_API int nv_embedding(const int* ids, const int* feed, const void* table, int table_dt, float* out, int T, int H, int V,
-                        int* err, cudaStream_t s) {
+                        int copies, int* err, cudaStream_t s) {
   if (!dt_ok(table_dt)) return NV_ERR_BAD_DTYPE;
+  if (copies < 1) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
-  NV_RETURN_IF(launch_dep(embedding_kernel, dim3(T), dim3(256), 0, s, ids, table, table_dt, out, H, V, err, feed));
+  NV_RETURN_IF(launch_dep(embedding_kernel, dim3(T), dim3(256), 0, s, ids, table, table_dt, out, H, V, err, feed,
+                          copies));
   NV_RETURN_LAST();
 }
 
@@ -616,14 +623,16 @@ NV_API int nv_paged_attention_plain(const void* qkv, int dt, int q_stride, const
 }
 
 NV_API int nv_router_topk(const float* logits, long long ld, int T, int E, int K, int renorm, int* idx,
-                          float* score, int C, const float* gate_logit, long long gate_ld, cudaStream_t s) {
-  if (K < 1 || K > E || K > 32 || C < 0 || C > 32 || (C > 0 && !gate_logit)) return NV_ERR_UNSUPPORTED;
+                          float* score, int C, const float* gate_logit, long long gate_ld, int mode,
+                          const float* choice_bias, float weight_scale, cudaStream_t s) {
+  if (K < 1 || K > E || K > 32 || C < 0 || C > 32 || mode < 0 || mode > 1) return NV_ERR_UNSUPPORTED;
   if (T == 0) return NV_OK;
   const int warps = 4;
   size_t smem = (size_t)warps * E * sizeof(double);
   if (smem > 48 * 1024) return NV_ERR_UNSUPPORTED;  // E <= 1536
   router_topk_kernel<<<(T + warps - 1) / warps, warps * 32, smem, s>>>(logits, ld, T, E, K, renorm, idx, score, C,
-                                                                       gate_logit, gate_ld);
+                                                                       gate_logit, gate_ld,
+                                                                       RouteRule{mode, choice_bias, weight_scale});
   NV_RETURN_LAST();
 }
 

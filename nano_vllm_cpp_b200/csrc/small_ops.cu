@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(
     int* __restrict__ pair_pos, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
     int* __restrict__ tile_rows, int* __restrict__ num_tiles, int* __restrict__ err,
     const bf16* __restrict__ x, bf16* __restrict__ x_sorted, int H, int n_static, int* __restrict__ zero,
-    int n_zero) {
+    int n_zero, RouteRule rule) {
   extern __shared__ double rs_smem[];
   grid_dep_wait();
   grid_dep_launch();
@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(
   const int KT = K + C;
   for (int t = warp; t < T; t += 32)
     route_row(logits + (size_t)t * ld, E, K, renorm, rs_smem + (size_t)warp * E, lane, idx + (size_t)t * KT,
-              score + (size_t)t * KT, C, C ? gate_logit + (size_t)t * gate_ld : nullptr);
+              score + (size_t)t * KT, C, (C && gate_logit) ? gate_logit + (size_t)t * gate_ld : nullptr, rule);
   __threadfence_block();
   __syncthreads();
   int* al_s = (int*)(rs_smem + (size_t)32 * E);
@@ -310,8 +310,9 @@ NV_API int nv_moe_route_small(const float* logits, long long ld, int T, int E, i
                               const float* gate_logit, long long gate_ld, int* idx, float* score, int tile_m,
                               int* counts, int* offsets, int* sorted_token, int* pair_pos, int* tile_expert,
                               int* tile_row0, int* tile_rows, int* num_tiles, int* err, const void* x,
-                              void* x_sorted, int H, int n_static, int* zero, int n_zero, cudaStream_t s) {
-  if (!nv_moe_route_small_usable(T, E, K, C, H) || K < 1 || K > E || (C > 0 && !gate_logit)) return NV_ERR_UNSUPPORTED;
+                              void* x_sorted, int H, int n_static, int* zero, int n_zero, int mode,
+                              const float* choice_bias, float weight_scale, cudaStream_t s) {
+  if (!nv_moe_route_small_usable(T, E, K, C, H) || K < 1 || K > E || mode < 0 || mode > 1) return NV_ERR_UNSUPPORTED;
   if (n_zero < 0 || n_zero > 1024 || (n_zero && !zero)) return NV_ERR_BAD_SIZE;
   if (n_static != 0 && n_static != C) return NV_ERR_UNSUPPORTED;
   if (T == 0) return NV_OK;
@@ -319,6 +320,6 @@ NV_API int nv_moe_route_small(const float* logits, long long ld, int T, int E, i
   NV_RETURN_IF(launch_dep(moe_route_small_kernel, dim3(1), dim3(1024), smem, s, logits, ld, T, E, K, renorm, C,
                           gate_logit, gate_ld, idx, score, tile_m, counts, offsets, sorted_token, pair_pos, tile_expert,
                           tile_row0, tile_rows, num_tiles, err, (const bf16*)x, (bf16*)x_sorted, H, n_static, zero,
-                          n_zero));
+                          n_zero, RouteRule{mode, choice_bias, weight_scale}));
   NV_RETURN_LAST();
 }

@@ -25,7 +25,10 @@ class PagedAttention(Mixer):
     over every q and k head before the rotation, with one weight vector per side shared by the heads (``qk_norm_eps``);
     a bias on the output projection (``out_bias``); a *sink* in every softmax, a key with the score ``sink_score``
     and no value, so that ``p_j = exp(s_j) / (exp(sink_score) + sum_i exp(s_i))``; a position encoding that pairs
-    neighbouring elements or scales its cosines and sines.  ``names`` gives the tensors' names where they are not
+    neighbouring elements or scales its cosines and sines; no value projection at all (``values_from_keys``: a key
+    head as projected, before its norm and rotation, is also the value head, and there is no v tensor); softmax
+    weights that stay float32 in the product with the values (``exact_weights``; the tensor-core kernels of the
+    default path round them to bfloat16).  ``names`` gives the tensors' names where they are not
     the usual ones (keys: q, k, v, o, q_bias, k_bias, v_bias, o_bias, q_norm, k_norm).  A layer that uses one of
     these options runs the general kernels (``ops.qk_prepare_store``, ``ops.paged_attention_general``).
     """
@@ -37,7 +40,7 @@ class PagedAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, bias: bool,
                  position: PartSpec, window: int = 0, scale: float | None = None, v_head_dim: int | None = None,
                  qk_norm_eps: float | None = None, out_bias: bool = False, sink_score: float | None = None,
-                 names: dict | None = None):
+                 names: dict | None = None, values_from_keys: bool = False, exact_weights: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         self.hidden, self.Hq, self.Hkv, self.D = hidden_size, num_heads, num_kv_heads, head_dim
@@ -48,7 +51,12 @@ class PagedAttention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(float(head_dim))
         self.position = build_part("position", position) if isinstance(position, PartSpec) else position
         self.names = dict(self._NAMES, **(names or {}))
-        self.general = (self.Dv != self.D or self.qk_norm_eps is not None or self.sink_score is not None
+        self.values_from_keys = bool(values_from_keys)
+        if self.values_from_keys and self.Dv != self.D:
+            raise ValueError("values that are the keys have the keys' head size")
+        if self.values_from_keys and bias:
+            raise ValueError("values that are the keys: biased projections are not supported")
+        self.general = (self.values_from_keys or bool(exact_weights) or self.Dv != self.D or self.qk_norm_eps is not None or self.sink_score is not None
                         or self.position.pairing != "halves" or self.position.amplitude != 1.0)
         if self.general:
             if head_dim < 1 or head_dim > 256 or self.Dv < 1 or self.Dv > 256:
@@ -63,6 +71,8 @@ class PagedAttention(Mixer):
         H, q, kv, vv, n = self.hidden, self.Hq * self.D, self.Hkv * self.D, self.Hkv * self.Dv, self.names
         s = {n["q"]: TensorSpec((q, H)), n["k"]: TensorSpec((kv, H)),
              n["v"]: TensorSpec((vv, H)), n["o"]: TensorSpec((H, self.Hq * self.Dv))}
+        if self.values_from_keys:
+            del s[n["v"]]
         if self.bias:
             s.update({n["q_bias"]: TensorSpec((q,), kind="vector"), n["k_bias"]: TensorSpec((kv,), kind="vector"),
                       n["v_bias"]: TensorSpec((vv,), kind="vector")})
@@ -79,7 +89,7 @@ class PagedAttention(Mixer):
         n = self.names
         self.position.load(fetch, ctx)
         # q, k and v rows are stacked so that one product makes all three (src/model.cpp:508-513)
-        self.qkv_weight = _cat([fetch(n["q"]), fetch(n["k"]), fetch(n["v"])])
+        self.qkv_weight = _cat([fetch(n["q"]), fetch(n["k"])] + ([] if self.values_from_keys else [fetch(n["v"])]))
         self.qkv_bias = None
         if self.bias:
             self.qkv_bias = _cat([fetch(n["q_bias"]), fetch(n["k_bias"]), fetch(n["v_bias"])])
@@ -129,7 +139,8 @@ class PagedAttention(Mixer):
         P = self.pad
         q = torch.empty((T, Hq * (P or D)), dtype=ctx.act_dtype, device=h.device)
         pos = self.position
-        ops.qk_prepare_store(proj, 0, Hq * D, (Hq + Hkv) * D, batch.positions, batch.row_entry, bt, self.q_norm,
+        # (values that are the keys are read where the keys are, as projected: the kernel norms and turns its own copy)
+        ops.qk_prepare_store(proj, 0, Hq * D, Hq * D if self.values_from_keys else (Hq + Hkv) * D, batch.positions, batch.row_entry, bt, self.q_norm,
                              self.k_norm, self.qk_norm_eps or 0.0, pos.inv_freq(), pos.rotary_dim,
                              pos.pairing == "interleaved", pos.amplitude, q, cache.k, cache.v, Hq, Hkv, D, Dv,
                              cache.write, ctx.err)

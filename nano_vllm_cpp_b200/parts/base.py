@@ -36,6 +36,7 @@ import torch
 class TensorSpec:
     shape: tuple
     init: str = "normal"      # "normal": N(0, std) | "ones": 1 (+ N(0, norm_std) if asked) | "zeros" | "near_zero": N(0, norm_std)
+                              # | "identity": the unit matrix | "mean": 1 / length
     kind: str = "matrix"      # "matrix" | "vector": vectors are held in float32 on the device
 
 

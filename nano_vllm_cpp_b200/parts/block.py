@@ -24,10 +24,13 @@ _DEFAULT_NAMES = {"norm1": "input_layernorm.", "mixer": "self_attn.", "norm2": "
 class LayerSpec:
     """One layer as data.  ``parts``: slot name -> ``PartSpec``; ``names``: slot name -> prefix of the slot's
     tensors inside the layer (a slot without an entry uses ``<slot>.``).  The slots of the pre-norm block may be
-    given as keywords: ``LayerSpec(norm1=..., mixer=..., norm2=..., feed_forward=...)``."""
+    given as keywords: ``LayerSpec(norm1=..., mixer=..., norm2=..., feed_forward=...)``.  ``params``: constants of
+    the arrangement itself."""
 
-    def __init__(self, arrangement: str = "prenorm", parts: dict | None = None, names: dict | None = None, **slots):
+    def __init__(self, arrangement: str = "prenorm", parts: dict | None = None, names: dict | None = None,
+                 params: dict | None = None, **slots):
         self.arrangement = arrangement
+        self.params = dict(params or {})         # the arrangement's own constants (how many copies of the stream, ...)
         self.parts = dict(parts or {})
         for slot, spec in slots.items():
             if not isinstance(spec, PartSpec):

@@ -82,17 +82,40 @@ class SparseMoeSwiGLU(FeedForward):
     ``routed = sum_k w_k * down_e(silu(gate_e(h)) * up_e(h))`` for k in rank order;
     ``shared = sigmoid(h . w_gate) * down_s(silu(gate_s(h)) * up_s(h))`` if there is a shared
     expert; the result is ``shared + routed``.
+
+    Other routers are options.  ``score="sigmoid"``: every expert's score is ``s = sigmoid(r)`` by itself, in
+    float32; the ``top_k`` largest ``s + correction`` are chosen (``choice_bias``: a learned vector ``correction``
+    [experts] that steers the choice only), and the weights are the chosen experts' ``s`` without it.  ``route_scale``
+    multiplies the weights.  ``shared_gate=False``: the shared expert has no gate and is added as it is.  ``names``
+    gives the tensors' names where they are not the usual ones (keys: router, correction, shared_gate, and the
+    patterns expert_gate, expert_up, expert_down with ``{}`` for the expert's number, shared_gate_proj, shared_up,
+    shared_down).
     """
     wants_f32_input = True
 
+    _NAMES = {"router": "gate.weight", "correction": "correction", "shared_gate": "shared_expert_gate.weight",
+              "expert_gate": "experts.{}.gate_proj.weight", "expert_up": "experts.{}.up_proj.weight",
+              "expert_down": "experts.{}.down_proj.weight", "shared_gate_proj": "shared_expert.gate_proj.weight",
+              "shared_up": "shared_expert.up_proj.weight", "shared_down": "shared_expert.down_proj.weight"}
+
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, intermediate_size: int,
-                 shared_intermediate_size: int = 0, renormalize: bool = False):
+                 shared_intermediate_size: int = 0, renormalize: bool = False, score: str = "softmax",
+                 route_scale: float = 1.0, choice_bias: bool = False, shared_gate: bool = True,
+                 names: dict | None = None):
         if not (1 <= top_k <= num_experts):
             raise ValueError("top_k must lie in 1..num_experts")
         if top_k > 32 or num_experts > 1536:
             raise ValueError("the router kernel takes up to 32 experts per row out of up to 1536")
         self.hidden, self.E, self.K = hidden_size, num_experts, top_k
         self.inter, self.shared_inter, self.renorm = intermediate_size, shared_intermediate_size, renormalize
+        if score not in ops.ROUTE_SCORES:
+            raise ValueError(f"score must be one of {sorted(ops.ROUTE_SCORES)}, found {score!r}")
+        if choice_bias and score != "sigmoid":
+            raise ValueError("a choice bias goes with sigmoid scores")
+        self.score, self.route_scale, self.choice_bias = score, float(route_scale), bool(choice_bias)
+        self.shared_gate = bool(shared_gate) and shared_intermediate_size > 0
+        self.names = dict(self._NAMES, **(names or {}))
+        self.rule = None                # what the routing kernels take beyond the softmax rule (set at load)
         self._align = {}
         self._counters = None
         self._captured = {}
@@ -102,29 +125,35 @@ class SparseMoeSwiGLU(FeedForward):
         self.last_alignment = None      # the permutation buffers of the latest forward (for statistics)
 
     def tensor_specs(self, available=None):
-        H, I, E, SI = self.hidden, self.inter, self.E, self.shared_inter
-        s = {"gate.weight": TensorSpec((E, H))}
+        H, I, E, SI, n = self.hidden, self.inter, self.E, self.shared_inter, self.names
+        s = {n["router"]: TensorSpec((E, H))}
+        if self.choice_bias:
+            s[n["correction"]] = TensorSpec((E,), init="zeros", kind="vector")
         if available is not None and available("experts.gate_up_proj"):  # stacked form, src/model.cpp:274-281
             s["experts.gate_up_proj"] = TensorSpec((E, 2 * I, H))
             s["experts.down_proj"] = TensorSpec((E, H, I))
         else:
             for e in range(E):
-                s[f"experts.{e}.gate_proj.weight"] = TensorSpec((I, H))
-                s[f"experts.{e}.up_proj.weight"] = TensorSpec((I, H))
-                s[f"experts.{e}.down_proj.weight"] = TensorSpec((H, I))
+                s[n["expert_gate"].format(e)] = TensorSpec((I, H))
+                s[n["expert_up"].format(e)] = TensorSpec((I, H))
+                s[n["expert_down"].format(e)] = TensorSpec((H, I))
         if SI > 0:
-            s["shared_expert.gate_proj.weight"] = TensorSpec((SI, H))
-            s["shared_expert.up_proj.weight"] = TensorSpec((SI, H))
-            s["shared_expert.down_proj.weight"] = TensorSpec((H, SI))
-            s["shared_expert_gate.weight"] = TensorSpec((1, H))
+            s[n["shared_gate_proj"]] = TensorSpec((SI, H))
+            s[n["shared_up"]] = TensorSpec((SI, H))
+            s[n["shared_down"]] = TensorSpec((H, SI))
+            if self.shared_gate:
+                s[n["shared_gate"]] = TensorSpec((1, H))
         return s
 
     def load(self, fetch, ctx):
         self.ctx = ctx
-        H, I, E, SI = self.hidden, self.inter, self.E, self.shared_inter
-        self.router = fetch("gate.weight")
+        H, I, E, SI, n = self.hidden, self.inter, self.E, self.shared_inter, self.names
+        self.router = fetch(n["router"])
+        bias = fetch(n["correction"]).float().contiguous() if self.choice_bias else None
+        if self.score != "softmax" or bias is not None or self.route_scale != 1.0:
+            self.rule = (self.score, bias, self.route_scale)
         stacked = fetch.has("experts.gate_up_proj")
-        first = fetch("experts.gate_up_proj") if stacked else fetch("experts.0.gate_proj.weight")
+        first = fetch("experts.gate_up_proj") if stacked else fetch(n["expert_gate"].format(0))
         # The shared expert as C more experts that every row visits: possible when its width is a whole
         # number of expert widths.  Its chunks then ride in the grouped products and need no launches of
         # their own.  Only the tensor-core path does this; the plain path keeps the shared expert apart.
@@ -140,18 +169,19 @@ class SparseMoeSwiGLU(FeedForward):
             self.w_down[:E].copy_(fetch("experts.down_proj"))
         else:
             for e in range(E):
-                self.w_gate_up[e, :I].copy_(first if e == 0 else fetch(f"experts.{e}.gate_proj.weight"))
-                self.w_gate_up[e, I:].copy_(fetch(f"experts.{e}.up_proj.weight"))
-                self.w_down[e].copy_(fetch(f"experts.{e}.down_proj.weight"))
+                self.w_gate_up[e, :I].copy_(first if e == 0 else fetch(n["expert_gate"].format(e)))
+                self.w_gate_up[e, I:].copy_(fetch(n["expert_up"].format(e)))
+                self.w_down[e].copy_(fetch(n["expert_down"].format(e)))
         del first
         if SI > 0:
-            sg, su = fetch("shared_expert.gate_proj.weight"), fetch("shared_expert.up_proj.weight")
-            sd = fetch("shared_expert.down_proj.weight")
-            self.sh_gate = fetch("shared_expert_gate.weight")
+            sg, su = fetch(n["shared_gate_proj"]), fetch(n["shared_up"])
+            sd = fetch(n["shared_down"])
+            self.sh_gate = fetch(n["shared_gate"]) if self.shared_gate else None
             # the gate's single row rides along with the router's rows: one product gives both logits
-            if self.sh_gate.dtype == self.router.dtype:
+            if self.shared_gate and self.sh_gate.dtype == self.router.dtype:
                 self.router_and_gate = torch.cat([self.router, self.sh_gate.reshape(1, -1)], dim=0).contiguous()
-            if self.virtual and sg.dtype == su.dtype == sd.dtype == self.w_gate_up.dtype and self.router_and_gate is not None:
+            if (self.virtual and sg.dtype == su.dtype == sd.dtype == self.w_gate_up.dtype
+                    and (self.router_and_gate is not None or not self.shared_gate)):
                 for c in range(self.virtual):
                     self.w_gate_up[E + c, :I].copy_(sg[c * I:(c + 1) * I])
                     self.w_gate_up[E + c, I:].copy_(su[c * I:(c + 1) * I])
@@ -215,9 +245,9 @@ class SparseMoeSwiGLU(FeedForward):
             zero, c0, c1 = self._counters, self._counters[0:1], self._counters[1:2]
         if fast and al.secondary is None and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden):
             x_sorted = ops.moe_route_small(logits, self.K, self.renorm, C, gate_logit, idx, score, al, ctx.err,
-                                           x=None, zero=zero)   # one block copies rows slower than the copy kernel does
+                                           x=None, zero=zero, rule=self.rule)   # one block copies rows slower than the copy kernel does
         else:
-            ops.router_topk(logits, self.K, self.renorm, idx, score, C, gate_logit)
+            ops.router_topk(logits, self.K, self.renorm, idx, score, C, gate_logit, rule=self.rule)
             ops.moe_align(idx, KT, al, ctx.err, spread_last=C if fast else 0, zero=zero)
         self.last_alignment = al
         wide = al.secondary                      # the tile list of the SwiGLU product, if it has one of its own
@@ -232,7 +262,7 @@ class SparseMoeSwiGLU(FeedForward):
         if self.shared_inter > 0 and not C:
             sact = linear(ctx, h, self.sh_gate_up, ctx.act_dtype, swiglu=True)
             shared = linear(ctx, sact, self.sh_down, torch.float32)
-            if gate_logit is None:
+            if gate_logit is None and self.shared_gate:
                 gate_logit = small_linear(ctx, h32, self.sh_gate)
         # the combination (src/hip_ops.hip:873-892) is left to whoever takes the branch: the next norm sums it
         return RowMix(y, al.pair_pos[:T * KT].view(T, KT), score, shared, gate_logit if shared is not None else None)
@@ -279,11 +309,11 @@ class SparseMoeSwiGLU(FeedForward):
                 self._counters = torch.zeros(2, dtype=torch.int32, device=dev)
             c0, c1 = self._counters[0:1], self._counters[1:2]
         if many:
-            ops.router_topk(logits, K, self.renorm, idx, score, C, gate_logit)
+            ops.router_topk(logits, K, self.renorm, idx, score, C, gate_logit, rule=self.rule)
             ops.moe_align(idx, KT, al, ctx.err, static_last=C, zero=self._counters)
         else:
             ops.moe_route_small(logits, K, self.renorm, C, gate_logit, idx, score, al, ctx.err, x=None, static=True,
-                                zero=self._counters if c0 is not None else None)
+                                zero=self._counters if c0 is not None else None, rule=self.rule)
         self.last_alignment = al
         x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
         ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True, counter=c0)

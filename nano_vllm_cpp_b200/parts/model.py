@@ -18,6 +18,7 @@ from .base import PartSpec, RunContext, TensorSpec, resolve_branch
 from .block import LayerSpec, build_layer
 from .linear import linear
 from .registry import build_part
+from .streams import StreamUpdate, read_streams
 
 
 @dataclass
@@ -40,6 +41,10 @@ class ModelSpec:
     lm_head_name: str = "lm_head.weight"
     init_std: float = 0.02
     norm_init_std: float = 0.0          # random-weights mode: norm weights are 1 + N(0, this)
+    layer_ids: Optional[list] = None    # what stands in layer_prefix for each layer; None = its index in ``layers``
+    streams: int = 1                    # copies of the residual stream (see parts.streams)
+    logit_scale: float = 1.0            # logits = head(x) * logit_scale, then, with a cap,
+    logit_softcap: float = 0.0          # logits = cap * tanh(logits / cap)
 
     def calls(self):
         if self.order is None:
@@ -78,6 +83,9 @@ class Model:
         self.layers = [build_layer(ls) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm)
         self.calls = spec.calls()
+        self.after_call = None      # a hook (call index, stream, pending) for whoever wants to look at the stream layer by layer
+        if spec.layer_ids is not None and len(spec.layer_ids) != len(spec.layers):
+            raise ValueError("layer_ids: one entry per layer")
         for i, c in enumerate(self.calls):
             if not (0 <= c.layer < len(self.layers)):
                 raise ValueError(f"call {i} names layer {c.layer}, which does not exist")
@@ -91,7 +99,7 @@ class Model:
     # ------------------------------------------------------------------ tensors
     def _named_parts(self):
         for i, layer in enumerate(self.layers):
-            lp = self.spec.layer_prefix.format(i)
+            lp = self.spec.layer_prefix.format(i if self.spec.layer_ids is None else self.spec.layer_ids[i])
             for sub, part in layer.parts():
                 yield lp + sub, part
         yield self.spec.final_norm_prefix, self.final_norm
@@ -136,13 +144,22 @@ class Model:
         """Runs the rows of ``batch`` through every call; returns float32 logits ``[wanted, vocab]``."""
         ctx = self.ctx
         ops.mark_step()
-        x = torch.empty((batch.T, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
-        ops.embedding(batch.input_ids, self.embed, x, ctx.err, feed=ctx.feed)
+        s = self.spec
+        x = torch.empty((batch.T, s.streams * s.hidden_size), dtype=torch.float32, device=ctx.device)
+        ops.embedding(batch.input_ids, self.embed, x, ctx.err, feed=ctx.feed, copies=s.streams)
         pending = None
         for i, c in enumerate(self.calls):
             pending = self.layers[c.layer].forward(x, pending, batch, cache.view(i))
-        h, _ = self.final_norm.forward(x, resolve_branch(self.final_norm, pending))
+            if self.after_call is not None:
+                self.after_call(i, x, pending)
+        if s.streams > 1 or isinstance(pending, StreamUpdate):
+            h, _ = read_streams(self.final_norm, x, s.streams, pending, None)       # the copies are summed
+        else:
+            h, _ = self.final_norm.forward(x, resolve_branch(self.final_norm, pending))
         n_want = batch.want_rows.numel()
         if n_want == 0:
-            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
-        return linear(ctx, h, self.lm_head, torch.float32, a_rows=batch.want_rows)
+            return torch.empty((0, s.vocab_size), dtype=torch.float32, device=ctx.device)
+        logits = linear(ctx, h, self.lm_head, torch.float32, a_rows=batch.want_rows)
+        if s.logit_scale != 1.0 or s.logit_softcap > 0:
+            ops.scale_softcap(logits, s.logit_scale, s.logit_softcap)
+        return logits

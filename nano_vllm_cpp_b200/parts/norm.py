@@ -1,4 +1,4 @@
-"""RMSNorm fused with the residual sum."""
+"""Norms fused with the residual sum: RMSNorm, and the dynamic tanh, which needs no statistics."""
 from __future__ import annotations
 
 import torch
@@ -60,4 +60,55 @@ class RMSNorm(Norm):
         return out, out32
 
 
+class DynamicTanh(Norm):
+    """``y = tanh(alpha * x) * gain + shift``: a norm without mean or variance, every element by itself.  ``alpha`` is
+    one number, ``gain`` and ``shift`` are vectors over the width; all three are learned and held in float32, and the
+    arithmetic is float32.  The sum of the pending branch into the stream happens in the same kernel.
+
+    ``read_streams`` is the same norm for a model that keeps several copies of its stream (``parts.streams``): the
+    kernel brings the copies up to date, reads them with the next sublayer's weights and norms what it read."""
+    accepts_mix = True
+
+    def __init__(self, size: int, weight_name: str = "weight", shift_name: str = "bias", alpha_name: str = "alpha"):
+        self.size = size
+        self.weight_name, self.shift_name, self.alpha_name = weight_name, shift_name, alpha_name
+
+    def tensor_specs(self, available=None):
+        return {self.weight_name: TensorSpec((self.size,), init="ones", kind="vector"),
+                self.shift_name: TensorSpec((self.size,), init="near_zero", kind="vector"),
+                self.alpha_name: TensorSpec((), init="ones", kind="vector")}
+
+    def load(self, fetch, ctx):
+        self.ctx = ctx
+        self.gain = fetch(self.weight_name).float().contiguous()
+        self.shift = fetch(self.shift_name).float().contiguous()
+        self.alpha = fetch(self.alpha_name).float().reshape(1).contiguous()
+
+    def _outputs(self, T, device, want_f32):
+        out = torch.empty((T, self.size), dtype=self.ctx.act_dtype, device=device)
+        out32 = None
+        if want_f32:
+            out32 = out if out.dtype == torch.float32 else torch.empty((T, self.size), dtype=torch.float32, device=device)
+        return out, out32
+
+    def read_streams(self, x, streams: int, branch, carry, write, read, want_f32: bool = False):
+        """``x`` [T, streams * size]: the copies, brought up to date in place with ``branch`` (a float32 matrix, a
+        ``RowMix`` or None) through ``carry`` and ``write``, then read with ``read`` (None: their plain sum) and
+        normed.  Returns (rows in the activation dtype, float32 copy or None)."""
+        out, out32 = self._outputs(x.shape[0], x.device, want_f32)
+        mix = None
+        if isinstance(branch, RowMix):
+            if branch.gate_logit is None and branch.index.shape[1] <= ops.STREAM_MAX_MIX:
+                mix, branch = branch.as_tuple(), None
+            else:
+                branch = branch.sum()
+        ops.stream_mix_norm(x, streams, branch=branch, mix=mix, carry=carry, write=write, read=read,
+                            norm=(self.alpha, self.gain, self.shift), out=out, out32=None if out32 is out else out32)
+        return out, out32
+
+    def forward(self, x, branch, want_f32=False):
+        return self.read_streams(x, 1, branch, None, None, None, want_f32)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)

@@ -9,13 +9,14 @@ MIXERS: dict = {}
 FEED_FORWARDS: dict = {}
 ARRANGEMENTS: dict = {}
 TOKEN_INPUTS: dict = {}
+CONNECTIONS: dict = {}
 
 _TABLES = {"norm": NORMS, "position": POSITION_ENCODINGS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS,
-           "arrangement": ARRANGEMENTS, "token_input": TOKEN_INPUTS}
+           "arrangement": ARRANGEMENTS, "token_input": TOKEN_INPUTS, "connection": CONNECTIONS}
 
 
 def register_part(family: str, kind: str, cls) -> None:
-    """``family``: norm, position, mixer, feed_forward, token_input or arrangement."""
+    """``family``: norm, position, mixer, feed_forward, token_input, connection or arrangement."""
     _TABLES[family][kind] = cls
 
 

@@ -12,19 +12,47 @@ from .registry import register_part
 class RotaryNeoX(PositionEncoding):
     """Pairs ``(d, d + rotary_dim/2)`` of the first ``rotary_dim`` elements of a head are turned by
     ``float(pos) * inv_freq[d]`` with ``inv_freq[d] = float(1 / theta^(2d / rotary_dim))``, the
-    power taken in double (src/model.cpp:416-419; kernel src/hip_ops.hip:431-450)."""
+    power taken in double (src/model.cpp:416-419; kernel src/hip_ops.hip:431-450).  ``rotary_dim`` may be smaller
+    than the head: the rest of the head passes unchanged.
 
-    def __init__(self, rotary_dim: int, theta: float):
-        if rotary_dim % 2:
+    ``scaling`` = dict(factor, low, high, original) stretches the long waves (the rule of the Llama 3.1 models):
+    with the wavelength ``l = 2 pi / f``, a frequency stays where ``l < original / high``, becomes ``f / factor``
+    where ``l > original / low``, and in between is ``(1 - s) f / factor + s f`` with
+    ``s = (original / l - low) / (high - low)``.  Computed in double, rounded once to float32."""
+
+    def __init__(self, rotary_dim: int, theta: float, scaling: dict | None = None):
+        if rotary_dim % 2 or rotary_dim < 0:
             raise ValueError("rotary_dim must be even")
         self.rotary_dim, self.theta = rotary_dim, float(theta)
+        self.scaling = dict(scaling) if scaling else None
+        if self.scaling:
+            for key in ("factor", "low", "high", "original"):
+                if key not in self.scaling:
+                    raise ValueError(f"rotary scaling needs '{key}'")
+            if float(self.scaling["high"]) == float(self.scaling["low"]):
+                raise ValueError("rotary scaling: 'high' and 'low' must differ")
         self._inv = None
+
+    def frequencies(self) -> list:
+        half = self.rotary_dim // 2
+        f = [1.0 / (self.theta ** ((2.0 * i) / self.rotary_dim)) for i in range(half)]
+        if self.scaling:
+            sc = self.scaling
+            factor, low, high, orig = float(sc["factor"]), float(sc["low"]), float(sc["high"]), float(sc["original"])
+            for i, fi in enumerate(f):
+                wave = 2.0 * math.pi / fi
+                if wave < orig / high:
+                    continue
+                if wave > orig / low:
+                    f[i] = fi / factor
+                else:
+                    s = (orig / wave - low) / (high - low)
+                    f[i] = (1.0 - s) * fi / factor + s * fi
+        return f
 
     def load(self, fetch, ctx):
         self.ctx = ctx
-        half = self.rotary_dim // 2
-        inv = [1.0 / (self.theta ** ((2.0 * i) / self.rotary_dim)) for i in range(half)]
-        self._inv = torch.tensor(inv, dtype=torch.float64).to(torch.float32).to(ctx.device)
+        self._inv = torch.tensor(self.frequencies() or [0.0], dtype=torch.float64).to(torch.float32).to(ctx.device)
 
     def inv_freq(self):
         return self._inv

@@ -112,6 +112,10 @@ class RandomSource:
             return torch.zeros(spec.shape, dtype=self.store_dtype, device=self.device)
         if spec.init == "near_zero":
             return self._draw(name, spec.shape, 0.0, self.norm_std)
+        if spec.init == "identity":             # a square matrix that changes nothing
+            return torch.eye(spec.shape[0], dtype=self.store_dtype, device=self.device)
+        if spec.init == "mean":                 # weights that average: 1 / length
+            return torch.full(tuple(spec.shape), 1.0 / max(1, spec.shape[0]), dtype=self.store_dtype, device=self.device)
         if spec.init == "ones":
             if self.norm_std > 0:
                 return self._draw(name, spec.shape, 1.0, self.norm_std)
