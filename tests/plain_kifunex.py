@@ -117,8 +117,18 @@ def route(h, W, p, r):
     return picks, choice
 
 
-def mixture(h, W, p, mlp):
-    picks, _ = route(h, W, p, mlp["router"])
+def choice_margins(choice, K):
+    """Per token: how far the last chosen expert's choice score lies above the first one left out (inf if none is)."""
+    if K >= choice.shape[1]:
+        return torch.full((choice.shape[0],), float("inf"), dtype=F64)
+    top = torch.sort(choice, dim=1, descending=True).values
+    return top[:, K - 1] - top[:, K]
+
+
+def mixture(h, W, p, mlp, margins=None):
+    picks, choice = route(h, W, p, mlp["router"])
+    if margins is not None:
+        margins.append(choice_margins(choice, int(mlp["router"]["top"])))
     out = torch.zeros(h.shape[0], W[p + "e0.down"].shape[0], dtype=F64)
     for t, chosen in enumerate(picks):
         for e, w in chosen:
@@ -144,9 +154,9 @@ def weight_owner(cfg, i):
 
 
 # ------------------------------------------------------------------------------ the whole model
-def forward(cfg, W, tokens, layer_sums=None):
+def forward(cfg, W, tokens, layer_sums=None, margins=None):
     """Logits [T, vocab] of a whole sequence.  ``layer_sums``: a list that receives the sum of the copies after
-    every layer."""
+    every layer; ``margins``: a list that receives every router's ``choice_margins``."""
     T = len(tokens)
     n = int(cfg.get("streams", 1))
     x = W["embed"][torch.tensor(tokens, dtype=torch.long)]
@@ -155,7 +165,7 @@ def forward(cfg, W, tokens, layer_sums=None):
         lp = f"l{weight_owner(cfg, i)}."
         X = connected(X, W, lp + "hc1.", lp + "norm1", lambda h: window_attention(h, W, lp + "mix.", L["mixer"]))
         if L.get("mlp"):
-            X = connected(X, W, lp + "hc2.", lp + "norm2", lambda h: mixture(h, W, lp + "mlp.", L["mlp"]))
+            X = connected(X, W, lp + "hc2.", lp + "norm2", lambda h: mixture(h, W, lp + "mlp.", L["mlp"], margins))
         if layer_sums is not None:
             layer_sums.append(X.sum(dim=1))
     x = dyt(X.sum(dim=1), *norm_of(W, "final.norm"))
@@ -263,6 +273,13 @@ def write_folder(cfg, W, folder):
         for b in blobs:
             f.write(b)
     return folder
+
+
+def greedy_generate(cfg, W, prompt, n):
+    seq = list(prompt)
+    for _ in range(n):
+        seq.append(int(torch.argmax(forward(cfg, W, seq)[-1])))
+    return seq[len(prompt):]
 
 
 def attention_layer(dim=32, heads=4, kv_heads=2, window=24, rot_dims=16, base=10000.0, scaling=None, scale=None,
