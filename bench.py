@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --design bizodra [--design-sizes s,m]     (another measurement, see ``design_bench``)
+    python bench.py --design bizodra|kifunex [--design-sizes s,m]     (another measurement, see ``design_bench``)
 
 Default run: the layer sizes of the Qwen1.5-MoE-A2.7B shape with random bfloat16 weights, a batch
 of 8 sequences each at a 2,048-token context; a step is one decode step of that batch.  ``value``
@@ -232,6 +232,43 @@ def dense_qwen_config(z):
                 tie_word_embeddings=False, qkv_bias=True)
 
 
+# --design kifunex: the same measurement for the Kifunex decoder beside the closest existing model at equal size: a
+# Qwen2-MoE decoder with the same width, depth, heads, head size, window, experts, experts per token, expert and
+# shared-expert widths and vocabulary.
+KIFUNEX_SIZES = {
+    "s": dict(width=1024, layers=4, heads=8, kv_heads=2, dim=128, window=1024, experts=16, top=4, ff=512, shared_ff=1024,
+              streams=2, vocab=32000),
+    "m": dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, window=1024, experts=32, top=4, ff=768, shared_ff=1536,
+              streams=2, vocab=32000),
+}
+
+
+def kifunex_config(z):
+    D = z["dim"]
+    mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": D, "vdim": D, "scale": D ** -0.5,
+             "mask": {"size": z["window"]},
+             "rot": {"dims": D // 2, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0},
+           "shared": {"ff": z["shared_ff"]}}
+    return {"architecture": "Kifunex", "vocab": z["vocab"], "width": z["width"], "streams": z["streams"],
+            "norm": {"eps": 1e-6}, "logit_scale": 1.0, "logit_softcap": 30.0,
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(z["layers"])]}
+
+
+def sparse_qwen_config(z):
+    return dict(architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe", num_hidden_layers=z["layers"],
+                hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+                head_dim=z["dim"], num_experts=z["experts"], num_experts_per_tok=z["top"],
+                moe_intermediate_size=z["ff"], shared_expert_intermediate_size=z["shared_ff"], intermediate_size=4 * z["ff"],
+                decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=False, use_sliding_window=True,
+                sliding_window=z["window"], max_window_layers=0, vocab_size=z["vocab"], rope_theta=1e6,
+                rms_norm_eps=1e-6, max_position_embeddings=32768, tie_word_embeddings=False, qkv_bias=True)
+
+
+DESIGNS = {"bizodra": (DESIGN_SIZES, "bizodra", bizodra_config, "qwen2_dense", dense_qwen_config),
+           "kifunex": (KIFUNEX_SIZES, "kifunex", kifunex_config, "qwen2_moe", sparse_qwen_config)}
+
+
 def design_bench(args) -> int:
     import torch
     from nano_vllm_cpp_b200.csrc import ops
@@ -258,9 +295,10 @@ def design_bench(args) -> int:
             ts.append(a.elapsed_time(b))
         return sorted(ts)[len(ts) // 2]
 
+    sizes, design_name, design_cfg, beside_name, beside_cfg = DESIGNS[args.design]
     for size in args.design_sizes.split(","):
-        z = DESIGN_SIZES[size]
-        for model, cfg in (("bizodra", bizodra_config(z)), ("qwen2_dense", dense_qwen_config(z))):
+        z = sizes[size]
+        for model, cfg in ((design_name, design_cfg(z)), (beside_name, beside_cfg(z))):
             work = tempfile.mkdtemp(prefix="bench_design_")
             with open(os.path.join(work, "config.json"), "w") as f:
                 json.dump(cfg, f)
@@ -347,7 +385,7 @@ def design_bench(args) -> int:
             rows.append(row)
             del runner
             torch.cuda.empty_cache()
-    print(json.dumps({"metric": "design_throughput", "design": "bizodra", "beside": "qwen2_dense", "dtype": "bf16",
+    print(json.dumps({"metric": "design_throughput", "design": design_name, "beside": beside_name, "dtype": "bf16",
                       "data": "synthetic", "peaks": {"source": peak_src, **P}, "steps": args.steps, "warmup": args.warmup,
                       "clocks": clocks.stop(), "rows": rows}))
     return 0
@@ -403,7 +441,7 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-kernel-times", action="store_true", help="skip the per-kernel-class CUDA-event times")
-    ap.add_argument("--design", default=None, choices=["bizodra"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="instead of the default workload: this design beside the closest existing model at equal size")
     ap.add_argument("--design-sizes", default="s,m", help="which of the sizes of --design to run, with commas")
     args = ap.parse_args()

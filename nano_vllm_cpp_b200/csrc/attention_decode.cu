@@ -708,7 +708,7 @@ NV_API int nv_attention_decode_splits(int rows, int Hq, int Hkv, int max_context
   for (int s = 1; s <= most; ++s) {
     const long long ctas = blocks * s;
     const long long waves = (ctas + slots - 1) / slots;
-    const double score = (double)ctas / ((double)waves * (double)slots) - 0.01 * s;
+    const double score = (double)ctas / ((double)waves * (double)slots) - 0.001 * s;
     if (score > best_score + 1e-9) { best_score = score; best = s; }
   }
   return best;

@@ -18,6 +18,11 @@
 // warps go from block to block without waiting for the tensor core, and the tensor core computes S while they
 // work.  Two CTAs share a multiprocessor and fill each other's gaps.  Every wait is bounded.
 //
+// TERMS = 3: the float32 weights P are not rounded for their product with the values.  Each is split into three
+// bfloat16 terms (hi, the rest, the rest of the rest: 24 bits), the softmax warps write three P tiles, and the
+// issuer adds three products P_t(i) V(i) into the same accumulator.  The three tiles take 48 KB, so with a head size
+// of 128 one CTA lives on a multiprocessor instead of two.
+//
 // Takes bfloat16, head_dim 64 or 128, pages of 16, 32 or 64 keys; everything else goes to the mma.sync kernel
 // (attention_prefill.cu), which is also this kernel's twin in the tests.  (The reference's kernel:
 // src/hip_ops.hip:473-551.)
@@ -51,7 +56,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-template <int D>
+template <int D, int TERMS>
 __global__ void __launch_bounds__(PT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                             const __grid_constant__ CUtensorMap tm_v, PtArgs a) {
@@ -67,7 +72,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   uint8_t* Qs = smem;
   uint8_t* Ks = Qs + SL * Q_SLAB;                  // two buffers
   uint8_t* Vs = Ks + 2 * SL * KV_SLAB;
-  uint8_t* Ps = Vs + SL * KV_SLAB;                 // [128 rows][64 keys] bf16
+  uint8_t* Ps = Vs + SL * KV_SLAB;                 // TERMS tiles of [128 rows][64 keys] bf16
+  constexpr uint32_t P_TILE = TQ * 128;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   // Which (tile, head) is this CTA's.  A causal tile's work grows with its place in the request, and two CTAs share
@@ -192,7 +198,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         }
 #pragma unroll
         for (int kk = 0; kk < TKB / 16; ++kk) dv[kk] = smem_desc_sw128_mn(v_addr + kk * 2048, KV_SLAB, 1024);
-        const uint64_t dp = smem_desc_sw128(p_addr);
+        uint64_t dp[TERMS];
+#pragma unroll
+        for (int t = 0; t < TERMS; ++t) dp[t] = smem_desc_sw128(p_addr + t * P_TILE);
         auto issue_s = [&](int i) {
           const int b = i & 1;
           mbar_wait(&k_full[b], (i >> 1) & 1, a.err, 0x7203);
@@ -211,7 +219,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
           mbar_wait(&v_full, i & 1, a.err, 0x7206);
           tc_fence_after();
           // 16 keys per product: 32 bytes (2 units) along P's rows, two 8-key groups (2,048 bytes = 128 units) of V
-          umma_bf16_x4s(tmem_o, dp, dv[0], idesc_o, i ? 1u : 0u, 2, 128);
+#pragma unroll
+          for (int t = 0; t < TERMS; ++t) umma_bf16_x4s(tmem_o, dp[t], dv[0], idesc_o, (i || t) ? 1u : 0u, 2, 128);
           umma_commit(&v_empty);
           umma_commit(&pv_done);
           if (i + 2 < n_blocks) issue_s(i + 2);      // into the buffer that S(i) has left
@@ -293,6 +302,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
           __nv_bfloat162 t3 = __floats2bfloat162_rn(s[c * 8 + 6], s[c * 8 + 7]);
           v.x = *(uint32_t*)&t0; v.y = *(uint32_t*)&t1; v.z = *(uint32_t*)&t2; v.w = *(uint32_t*)&t3;
           *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = v;
+          if (TERMS > 1) {
+            // what the rounding dropped, twice over: p = hi + mid + lo to all of float32's bits
+            float rest[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) rest[u] = s[c * 8 + u] - __bfloat162float(__float2bfloat16_rn(s[c * 8 + u]));
+#pragma unroll
+            for (int t = 1; t < TERMS; ++t) {
+              __nv_bfloat162 w0 = __floats2bfloat162_rn(rest[0], rest[1]), w1 = __floats2bfloat162_rn(rest[2], rest[3]);
+              __nv_bfloat162 w2 = __floats2bfloat162_rn(rest[4], rest[5]), w3 = __floats2bfloat162_rn(rest[6], rest[7]);
+              v.x = *(uint32_t*)&w0; v.y = *(uint32_t*)&w1; v.z = *(uint32_t*)&w2; v.w = *(uint32_t*)&w3;
+              *(uint4*)(prow + t * P_TILE + ((c ^ (r & 7)) << 4)) = v;
+#pragma unroll
+              for (int u = 0; u < 8; ++u) rest[u] -= __bfloat162float(__float2bfloat16_rn(rest[u]));
+            }
+          }
         }
         fence_async_smem();
         tc_fence_before();
@@ -328,7 +352,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   if (warp == 1) tmem_dealloc(tmem_base, 256);
 }
 
-template <int D>
+template <int D, int TERMS>
 int launch_prefill_tc(const PtArgs& a, const void* qkv, int q_stride, int T, const void* kc, const void* vc,
                       int num_pages, int max_tiles, cudaStream_t s) {
   CUtensorMap tm_q, tm_k, tm_v;
@@ -340,16 +364,16 @@ int launch_prefill_tc(const PtArgs& a, const void* qkv, int q_stride, int T, con
   rc = nv_tensor_map_bf16(vc, rows, D, D, a.page, &tm_v);
   if (rc) return rc;
   constexpr int SL = D / 64;
-  const size_t smem = (size_t)SL * TQ * 128 + 3 * (size_t)SL * TKB * 128 + (size_t)TQ * 128 + 1024;
+  const size_t smem = (size_t)SL * TQ * 128 + 3 * (size_t)SL * TKB * 128 + (size_t)TERMS * TQ * 128 + 1024;
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, TERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
   dim3 grid(max_tiles > 0 ? max_tiles : 1, a.Hq);
-  NV_RETURN_IF(launch_dep(attention_prefill_tc_kernel<D>, grid, dim3(PT_THREADS), smem, s, tm_q, tm_k, tm_v, a));
+  NV_RETURN_IF(launch_dep(attention_prefill_tc_kernel<D, TERMS>, grid, dim3(PT_THREADS), smem, s, tm_q, tm_k, tm_v, a));
   NV_RETURN_LAST();
 }
 
@@ -366,8 +390,9 @@ NV_API int nv_attention_prefill_tc_usable(int D, int page) {
 NV_API int nv_attention_prefill_tc(const void* qkv, int q_stride, int T, const void* kc, const void* vc, int num_pages,
                                    const int* block_table, int max_blocks, const int* cu_rows, const int* entry_pos0,
                                    int S, int max_tiles, float scale, int window, void* out, int Hq, int Hkv, int D,
-                                   int page, int min_rows, int* err, cudaStream_t stream) {
+                                   int page, int min_rows, int weight_terms, int* err, cudaStream_t stream) {
   if (!nv_attention_prefill_tc_usable(D, page) || Hkv <= 0 || Hq % Hkv) return NV_ERR_UNSUPPORTED;
+  if (weight_terms != 1 && weight_terms != 3) return NV_ERR_UNSUPPORTED;
   if (q_stride % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15)) return NV_ERR_UNSUPPORTED;
   if (S == 0 || max_tiles == 0 || T == 0) return NV_OK;
   PtArgs a;
@@ -384,6 +409,10 @@ NV_API int nv_attention_prefill_tc(const void* qkv, int q_stride, int T, const v
   }
   a.first_wave = num_sms;
   const int tiles = (max_tiles + S + 1) / 2;
-  if (D == 64) return launch_prefill_tc<64>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
-  return launch_prefill_tc<128>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
+  if (weight_terms == 3) {
+    if (D == 64) return launch_prefill_tc<64, 3>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
+    return launch_prefill_tc<128, 3>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
+  }
+  if (D == 64) return launch_prefill_tc<64, 1>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
+  return launch_prefill_tc<128, 1>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
 }

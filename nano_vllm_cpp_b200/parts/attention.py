@@ -147,8 +147,9 @@ class PagedAttention(Mixer):
         att = torch.empty((T, Hq * (P or Dv)), dtype=ctx.act_dtype, device=h.device)
         if P:
             # Entries of one row go to the split-key decode kernel (its form that keeps the weights float32), the
-            # others to the tensor-core kernel, where the float32 weights enter the product with the values as three
-            # bfloat16 terms; both add the sink to the softmax's denominator.
+            # others to a tensor-core kernel (tcgen05 for head sizes 64 and 128 without a sink, else mma.sync), where
+            # the float32 weights enter the product with the values as three bfloat16 terms; the decode kernel and
+            # the mma.sync kernel add the sink to the softmax's denominator.
             single = batch.n_single if ops.attention_decode_usable(cache.k, P) else 0
             if single:
                 ops.attention_decode(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale, self.window,
@@ -158,7 +159,8 @@ class PagedAttention(Mixer):
             if single < batch.S:
                 tiles = (batch.T - single) // ops.attention_prefill_tile_rows() + (batch.S - single)
                 ops.attention_prefill(q, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
-                                      self.window, att, Hq, Hkv, P, err=ctx.err, kernel="mma", min_rows=2 if single else 1,
+                                      self.window, att, Hq, Hkv, P, err=ctx.err, min_rows=2 if single else 1,
+                                      kernel="mma" if self.sink_score is not None else "auto",
                                       sink_score=self.sink_score, weight_terms=3)
         else:
             ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,

@@ -344,6 +344,57 @@ def test_one_key_stands_out(window, i, gap, decoded, dtype):
     assert float((other[i] - want[i]).abs().max()) > 0.2 * float(want.abs().max())
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_softmax_weights_keep_their_bits_in_the_product_with_the_values(D):
+    """Values of alternating sign and large size under nearly equal weights: the sum cancels, and weights rounded to
+    bfloat16 would show in it (the test computes that they would, on a third of the values); the three-term kernels
+    for prompts (tcgen05 and mma.sync) and the decode kernel's float32-weights form stay inside the rounding of
+    their bfloat16 output."""
+    from nano_vllm_cpp_b200.csrc import ops
+    T, Hq, page, scale = 200, 2, 16, D ** -0.5
+    g = torch.Generator().manual_seed(5)
+    q = (0.3 * torch.randn(T, Hq, D, generator=g)).to(torch.bfloat16)
+    k = torch.randn(T, D, generator=g).to(torch.bfloat16)
+    sign = torch.tensor([1.0 if j % 2 == 0 else -1.0 for j in range(T)])
+    v = (sign[:, None] * 48.0 + torch.randn(T, D, generator=g)).to(torch.bfloat16)
+    s = torch.einsum("thd,jd->htj", q.double(), k.double()) * scale
+    s = s.masked_fill(~torch.tril(torch.ones(T, T, dtype=torch.bool)), -1e30)
+    ref = torch.einsum("htj,jd->thd", torch.softmax(s, dim=2), v.double())
+    bound = 2 ** -8 * ref.abs() + 2e-3
+    e = torch.exp(s - s.max(dim=2, keepdim=True).values)
+    rounded = torch.einsum("htj,jd->thd", e.float().to(torch.bfloat16).double() / e.sum(dim=2, keepdim=True), v.double())
+    assert float(((rounded - ref).abs() > bound)[20:].float().mean()) > 0.2       # the case shows what it is meant to
+    n_pages = (T + page - 1) // page
+    table = [(7 * i + 2) % 29 for i in range(n_pages)]
+    kc = torch.zeros(29, 1, page, D, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    for i, pg in enumerate(table):
+        n = min(page, T - i * page)
+        kc[pg, 0, :n] = k[i * page:i * page + n].to(DEV)
+        vc[pg, 0, :n] = v[i * page:i * page + n].to(DEV)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    bt = torch.tensor([table], **i32)
+    qd = q.reshape(T, Hq * D).to(DEV).contiguous()
+    err = ops.ErrorFlag(DEV)
+    tiles = T // ops.attention_prefill_tile_rows() + 1
+    for kernel in ("auto", "mma"):
+        out = torch.zeros(T, Hq * D, dtype=torch.bfloat16, device=DEV)
+        ops.attention_prefill(qd, kc, vc, bt, torch.tensor([0, T], **i32), torch.tensor([0], **i32), tiles, scale, 0, out,
+                              Hq, 1, D, err=err, kernel=kernel, weight_terms=3)
+        err.check(kernel)
+        worst = float(((out.double().cpu().view(T, Hq, D) - ref).abs() / bound).max())
+        assert worst <= 1.0, f"{kernel}: {worst:.2f} times the bound"
+    rows = list(range(T - 5, T))
+    out = torch.zeros(len(rows), Hq * D, dtype=torch.bfloat16, device=DEV)
+    for splits_ctx in (T, 4096):                   # (the longest context fixes the number of key splits)
+        ops.attention_decode(qd[rows].contiguous(), kc, vc, bt.repeat(len(rows), 1).contiguous(),
+                             torch.arange(len(rows), **i32), torch.tensor(rows, **i32), scale, 0, out, Hq, 1, D, splits_ctx,
+                             err=err, float_weights=True)
+        err.check("decode")
+        worst = float(((out.double().cpu().view(len(rows), Hq, D) - ref[rows]).abs() / bound[rows]).max())
+        assert worst <= 1.0, f"decode: {worst:.2f} times the bound"
+
+
 def route_case(E, K, T, seed, spread):
     g = torch.Generator().manual_seed(seed)
     W = {"m.router": torch.randn(E, 48, generator=g, dtype=F64) / 4, "m.correction": spread * torch.randn(E, generator=g, dtype=F64)}
