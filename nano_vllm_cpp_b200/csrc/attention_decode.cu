@@ -352,7 +352,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 constexpr int TC_ROWS = 16;      // query heads per block (rows of the MMA)
 
 // D: head dimension, a multiple of 64 (compile time: it sizes the fragments).
-template <int D>
+template <int D, int TERMS>
 __global__ void __launch_bounds__((WARPS + 1) * 32, D <= 128 ? 3 : 1)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                            DecArgs a) {
@@ -523,8 +523,21 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             o[i2][0] *= al_lo; o[i2][1] *= al_lo; o[i2][2] *= al_hi; o[i2][3] *= al_hi;
           }
         }
-        uint32_t pa[4] = {pack_bf16(s0[0], s0[1]), pack_bf16(s0[2], s0[3]), pack_bf16(s1[0], s1[1]),
-                          pack_bf16(s1[2], s1[3])};
+        // TERMS = 3: the float32 weights are split into three bfloat16 terms (hi, the rest, the rest of the rest:
+        // all 24 bits), and each term is multiplied with the values into the same accumulators
+        uint32_t pa[TERMS][4];
+        {
+          float w[8] = {s0[0], s0[1], s0[2], s0[3], s1[0], s1[1], s1[2], s1[3]};
+#pragma unroll
+          for (int tm = 0; tm < TERMS; ++tm) {
+            pa[tm][0] = pack_bf16(w[0], w[1]); pa[tm][1] = pack_bf16(w[2], w[3]);
+            pa[tm][2] = pack_bf16(w[4], w[5]); pa[tm][3] = pack_bf16(w[6], w[7]);
+            if (tm + 1 < TERMS) {
+#pragma unroll
+              for (int u = 0; u < 8; ++u) w[u] -= __bfloat162float(__float2bfloat16_rn(w[u]));
+            }
+          }
+        }
         {
           const int key = kb * 16 + (lane % 8) + 8 * ((lane / 8) % 2);
           const uint32_t rowaddr = vbase + key * 128;
@@ -539,8 +552,11 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              mma16816(o[2 * (d4 * 4 + u)], pa, b[u][0], b[u][1]);
-              mma16816(o[2 * (d4 * 4 + u) + 1], pa, b[u][2], b[u][3]);
+#pragma unroll
+              for (int tm = 0; tm < TERMS; ++tm) {
+                mma16816(o[2 * (d4 * 4 + u)], pa[tm], b[u][0], b[u][1]);
+                mma16816(o[2 * (d4 * 4 + u) + 1], pa[tm], b[u][2], b[u][3]);
+              }
             }
           }
         }
@@ -643,7 +659,7 @@ int launch_decode(const DecArgs& a, int R, int G, size_t smem, cudaStream_t s) {
   return G == 1 ? launch_decode_g<TC, CPL, 1>(a, R, G, smem, s) : launch_decode_g<TC, CPL, 4>(a, R, G, smem, s);
 }
 
-template <int D>
+template <int D, int TERMS>
 int launch_decode_tc(DecArgs a, int R, const void* kc, const void* vc, int num_pages, float scale, cudaStream_t s) {
   const int G = a.Hq / a.Hkv;
   CUtensorMap tm_k, tm_v;
@@ -658,17 +674,17 @@ int launch_decode_tc(DecArgs a, int R, const void* kc, const void* vc, int num_p
   const size_t smem = (ring > merge ? ring : merge) + 1024;
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tc_kernel<D, TERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          160 * 1024);
     if (e != cudaSuccess) return (int)e;
     // three CTAs with a 64 KB ring each need nearly all of a multiprocessor's shared memory
-    e = cudaFuncSetAttribute(attention_decode_tc_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    e = cudaFuncSetAttribute(attention_decode_tc_kernel<D, TERMS>, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
   dim3 grid(R, a.Hkv * ((G + TC_ROWS - 1) / TC_ROWS), a.splits);
-  NV_RETURN_IF(launch_dep(attention_decode_tc_kernel<D>, grid, dim3((WARPS + 1) * 32), smem, s, tm_k, tm_v, a));
+  NV_RETURN_IF(launch_dep(attention_decode_tc_kernel<D, TERMS>, grid, dim3((WARPS + 1) * 32), smem, s, tm_k, tm_v, a));
   NV_RETURN_LAST();
 }
 
@@ -724,9 +740,9 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
                                int Hkv, int D, int page, int num_pages, int splits, float* scratch, int* err,
                                int* split_count, int split_count_len, int has_sink, float sink_score,
                                int float_weights, cudaStream_t stream) {
-  // has_sink: a further key with the score sink_score and no value in every softmax.  float_weights: the weights
-  // stay float32 in their product with the values (the lane-per-chunk kernel; the tensor-core form rounds them to
-  // bfloat16).  Either one keeps the tensor-core form out.
+  // has_sink: a further key with the score sink_score and no value in every softmax; it keeps the tensor-core form
+  // out.  float_weights: the weights keep all their bits in their product with the values (the lane-per-chunk
+  // kernel multiplies in float32; the tensor-core form takes them as three bfloat16 terms instead of one).
   if (!dt_ok(q_dt) || !dt_ok(cache_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
   if (D <= 0 || D > 256 || D % 8 || Hkv <= 0 || Hq % Hkv || page % 16) return NV_ERR_UNSUPPORTED;
   const int esize = cache_dt == NV_DT_BF16 ? 2 : 4;
@@ -759,14 +775,20 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   // next page is on its way while it works on one (with one stage per warp a warp sat out the whole memory latency
   // between two pages), and three CTAs of 76 KB still share a multiprocessor.  Deeper rings lose CTAs and time.
   int tc_stages = stages / WARPS * WARPS;
-  if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS && !has_sink &&
-      !float_weights) {
+  if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS && !has_sink) {
     a.stages = tc_stages;
-    // tensor-core form (a page of keys per warp); its blocks take up to 16 query heads of a kv head
-    rc = D == 64 ? launch_decode_tc<64>(a, R, kc, vc, num_pages, scale, stream)
-       : D == 128 ? launch_decode_tc<128>(a, R, kc, vc, num_pages, scale, stream)
-       : D == 192 ? launch_decode_tc<192>(a, R, kc, vc, num_pages, scale, stream)
-                  : launch_decode_tc<256>(a, R, kc, vc, num_pages, scale, stream);
+    // tensor-core form (a page of keys per warp); its blocks take up to 16 query heads of a kv head; with
+    // float_weights the weights enter the product with the values as three bfloat16 terms
+    if (float_weights)
+      rc = D == 64 ? launch_decode_tc<64, 3>(a, R, kc, vc, num_pages, scale, stream)
+         : D == 128 ? launch_decode_tc<128, 3>(a, R, kc, vc, num_pages, scale, stream)
+         : D == 192 ? launch_decode_tc<192, 3>(a, R, kc, vc, num_pages, scale, stream)
+                    : launch_decode_tc<256, 3>(a, R, kc, vc, num_pages, scale, stream);
+    else
+      rc = D == 64 ? launch_decode_tc<64, 1>(a, R, kc, vc, num_pages, scale, stream)
+         : D == 128 ? launch_decode_tc<128, 1>(a, R, kc, vc, num_pages, scale, stream)
+         : D == 192 ? launch_decode_tc<192, 1>(a, R, kc, vc, num_pages, scale, stream)
+                    : launch_decode_tc<256, 1>(a, R, kc, vc, num_pages, scale, stream);
   } else if (cache_dt == NV_DT_BF16) {
     rc = D <= 64 ? launch_decode<bf16, 1>(a, R, G, smem, stream)
                  : (D <= 128 ? launch_decode<bf16, 2>(a, R, G, smem, stream)
