@@ -61,7 +61,9 @@ __device__ __forceinline__ void st_cols(float* p, const Cols<VEC>& c) {
   }
 }
 
-template <int VEC>
+// SMAX: the most copies this instance keeps in registers (1, 2, 4 or 8): a thread's registers, and with them how many
+// blocks share a multiprocessor, follow the model's number of copies and not the largest number allowed.
+template <int VEC, int SMAX>
 __global__ void __launch_bounds__(SM_THREADS) stream_mix_norm_kernel(StreamArgs a) {
   __shared__ float s_carry[SM_MAX_STREAMS * SM_MAX_STREAMS], s_write[SM_MAX_STREAMS], s_read[SM_MAX_STREAMS];
   __shared__ int s_idx[SM_MAX_R];
@@ -83,9 +85,9 @@ __global__ void __launch_bounds__(SM_THREADS) stream_mix_norm_kernel(StreamArgs 
   if (c * VEC >= a.H) return;
   const size_t col = (size_t)c * VEC;
   float* xr = a.x + (size_t)t * S * a.H + col;
-  Cols<VEC> xs[SM_MAX_STREAMS];
+  Cols<VEC> xs[SMAX];
 #pragma unroll
-  for (int s = 0; s < SM_MAX_STREAMS; ++s)
+  for (int s = 0; s < SMAX; ++s)
     if (s < S) xs[s] = ld_cols<VEC>(xr + (size_t)s * a.H);
   if (a.update) {
     Cols<VEC> y;
@@ -115,14 +117,14 @@ __global__ void __launch_bounds__(SM_THREADS) stream_mix_norm_kernel(StreamArgs 
         for (int j = 0; j < VEC; ++j) y.v[j] += d.v[j];
       }
     }
-    Cols<VEC> nx[SM_MAX_STREAMS];
+    Cols<VEC> nx[SMAX];
 #pragma unroll
-    for (int d = 0; d < SM_MAX_STREAMS; ++d) {
+    for (int d = 0; d < SMAX; ++d) {
       if (d < S) {
 #pragma unroll
         for (int j = 0; j < VEC; ++j) nx[d].v[j] = s_write[d] * y.v[j];
 #pragma unroll
-        for (int s = 0; s < SM_MAX_STREAMS; ++s)
+        for (int s = 0; s < SMAX; ++s)
           if (s < S) {
             const float m = s_carry[s * S + d];
 #pragma unroll
@@ -131,7 +133,7 @@ __global__ void __launch_bounds__(SM_THREADS) stream_mix_norm_kernel(StreamArgs 
       }
     }
 #pragma unroll
-    for (int d = 0; d < SM_MAX_STREAMS; ++d)
+    for (int d = 0; d < SMAX; ++d)
       if (d < S) {
         xs[d] = nx[d];
         st_cols<VEC>(xr + (size_t)d * a.H, xs[d]);
@@ -142,7 +144,7 @@ __global__ void __launch_bounds__(SM_THREADS) stream_mix_norm_kernel(StreamArgs 
 #pragma unroll
   for (int j = 0; j < VEC; ++j) u.v[j] = 0.f;
 #pragma unroll
-  for (int s = 0; s < SM_MAX_STREAMS; ++s)
+  for (int s = 0; s < SMAX; ++s)
     if (s < S) {
 #pragma unroll
       for (int j = 0; j < VEC; ++j) u.v[j] = fmaf(s_read[s], xs[s].v[j], u.v[j]);
@@ -209,8 +211,16 @@ NV_API int nv_stream_mix_norm(float* x, int T, int S, int H, const float* branch
   int threads = 32;
   while (threads < SM_THREADS && threads < chunks) threads *= 2;
   const dim3 grid((unsigned)T, (unsigned)((chunks + threads - 1) / threads));
-  if (vec == 4) NV_RETURN_IF(launch_dep(stream_mix_norm_kernel<4>, grid, dim3(threads), 0, s, a));
-  else NV_RETURN_IF(launch_dep(stream_mix_norm_kernel<1>, grid, dim3(threads), 0, s, a));
+#define NV_STREAM_LAUNCH(SMAX)                                                                              \
+  do {                                                                                                      \
+    if (vec == 4) NV_RETURN_IF(launch_dep(stream_mix_norm_kernel<4, SMAX>, grid, dim3(threads), 0, s, a)); \
+    else NV_RETURN_IF(launch_dep(stream_mix_norm_kernel<1, SMAX>, grid, dim3(threads), 0, s, a));          \
+  } while (0)
+  if (S == 1) NV_STREAM_LAUNCH(1);
+  else if (S == 2) NV_STREAM_LAUNCH(2);
+  else if (S <= 4) NV_STREAM_LAUNCH(4);
+  else NV_STREAM_LAUNCH(8);
+#undef NV_STREAM_LAUNCH
   NV_RETURN_LAST();
 }
 
