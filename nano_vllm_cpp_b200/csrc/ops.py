@@ -379,8 +379,9 @@ def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, s
                      float_weights: bool = False) -> None:
     """One query row per request (``rows``: which batch rows; None = all) against its paged keys.  ``qkv``: rows
     whose first Hq * D elements are the query heads.  ``sink_score``: a further key with that score and no value
-    in every softmax.  ``float_weights``: the weights stay float32 in the product with the values (the kernel
-    that gives a lane a chunk of a key; the tensor-core form rounds them to bfloat16)."""
+    in every softmax.  ``float_weights``: the weights keep all their bits in the product with the values (the
+    tensor-core form takes them as three bfloat16 terms instead of one rounded one; the kernel that gives a lane a
+    chunk of a key, which other head sizes and a sink go to, multiplies in float32)."""
     _cuda_contig(qkv, k_cache, v_cache, block_table, row_entry, positions, out, rows)
     _i32(block_table, row_entry, positions, rows)
     R = qkv.shape[0] if rows is None else rows.numel()

@@ -146,7 +146,7 @@ class PagedAttention(Mixer):
                              cache.write, ctx.err)
         att = torch.empty((T, Hq * (P or Dv)), dtype=ctx.act_dtype, device=h.device)
         if P:
-            # Entries of one row go to the split-key decode kernel (its form that keeps the weights float32), the
+            # Entries of one row go to the split-key decode kernel (with weights that keep their float32 bits), the
             # others to a tensor-core kernel (tcgen05 for head sizes 64 and 128 without a sink, else mma.sync), where
             # the float32 weights enter the product with the values as three bfloat16 terms; the decode kernel and
             # the mma.sync kernel add the sink to the softmax's denominator.

@@ -284,7 +284,11 @@ MIXERS = [pk.attention_layer(dim=32, heads=4, kv_heads=2, window=24, rot_dims=16
           pk.attention_layer(dim=48, heads=3, kv_heads=3, window=17, rot_dims=48, base=500.0, scale=0.11)["mixer"],
           pk.attention_layer(dim=64, heads=8, kv_heads=1, window=40, rot_dims=0, scale=0.125)["mixer"],
           pk.attention_layer(dim=40, heads=2, kv_heads=1, window=1, rot_dims=20, scale=0.3)["mixer"],
-          pk.attention_layer(dim=128, heads=2, kv_heads=2, window=64, rot_dims=64, scale=0.09)["mixer"]]
+          pk.attention_layer(dim=128, heads=2, kv_heads=2, window=64, rot_dims=64, scale=0.09)["mixer"],
+          pk.attention_layer(dim=64, heads=20, kv_heads=1, window=30, rot_dims=32, scale=0.12)["mixer"],
+          pk.attention_layer(dim=192, heads=2, kv_heads=1, window=50, rot_dims=96, scaling=SCALING, scale=0.07)["mixer"],
+          pk.attention_layer(dim=96, heads=3, kv_heads=1, window=21, rot_dims=48, scale=0.1)["mixer"],
+          pk.attention_layer(dim=256, heads=1, kv_heads=1, window=35, rot_dims=256, scale=0.06)["mixer"]]
 CUTS = [[(0, 37), (0, 2)], [(37, 38), (2, 19)], [(38, 40), (19, 20)], [(40, 41), (20, 21)], [None, (21, 50)],
         [(41, 64), (50, 51)], [(64, 65), None], [(65, 66), None]]
 PAGES = [[7, 3, 11, 0, 9], [5, 2, 8, 10]]
@@ -326,7 +330,7 @@ def edge_case(window, T, i, j, width=64):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("decoded", [False, True])
 @pytest.mark.parametrize("window,i,gap", [(24, 50, 23), (24, 50, 24), (16, 47, 15), (16, 47, 16), (17, 33, 16), (17, 33, 17),
-                                          (400, 330, 327), (400, 330, 17)])
+                                          (400, 330, 327), (400, 330, 17), (300, 650, 299), (300, 650, 300)])
 def test_one_key_stands_out(window, i, gap, decoded, dtype):
     """A key just inside the window (gap = window - 1) takes half of row i's weight, a key just outside it
     (gap = window) takes none; at page borders, in a prompt and when row i is decoded alone after single rows; and a
@@ -335,6 +339,7 @@ def test_one_key_stands_out(window, i, gap, decoded, dtype):
     m, W, x = edge_case(window, T, i, i - gap)
     part, cache, ctx = attention_setup(m, 64, W, dtype)
     table = [(5 * p + 3) % 47 for p in range((T + 15) // 16)]
+    assert len(set(table)) == len(table)
     cuts = [[(0, T)]] if not decoded else [[(0, i - 2)]] + [[(t, t + 1)] for t in range(i - 2, T)]
     got = run_cut(part, cache, [x], cuts, dtype, [table], ctx)[0]
     want = pk.window_attention(x, W, "m.", m)
@@ -435,7 +440,9 @@ def test_router_alone(E, K, spread):
 
 MLPS = [pk.moe(experts=6, top=2, ff=24, shared_ff=24, scale=1.25), pk.moe(experts=5, top=5, ff=40, shared_ff=16, scale=0.5),
         pk.moe(experts=8, top=1, ff=32, shared_ff=0, scale=2.0), pk.moe(experts=4, top=3, ff=16, shared_ff=32, scale=1.0),
-        pk.moe(experts=3, top=2, ff=20, shared_ff=12, scale=1.0)]
+        pk.moe(experts=3, top=2, ff=20, shared_ff=12, scale=1.0),
+        dict(pk.moe(experts=16, top=4, ff=128, shared_ff=256, scale=1.5), width=256),      # sizes the tensor-core products take
+        dict(pk.moe(experts=12, top=3, ff=64, shared_ff=64, scale=0.8), width=128)]
 
 
 @pytest.mark.parametrize("fast", [True, False])
@@ -445,7 +452,8 @@ def test_mixture_alone(dtype, mlp, fast):
     """The feed-forward with one row, a handful, and more rows than the one-launch routing takes; a shared expert as
     wide as an expert, twice as wide, of a width of its own, and none; widths the tensor-core product refuses."""
     from nano_vllm_cpp_b200.parts import build_part, PartSpec
-    width = 64
+    mlp = dict(mlp)
+    width = mlp.pop("width", 64)
     cfg = pk.model_config([pk.attention_layer(mlp=mlp)], width=width, vocab=8)
     W = {k.replace("l0.mlp.", "m."): v for k, v in pk.make_weights(cfg, 51).items() if k.startswith("l0.mlp.")}
     ff = build_part("feed_forward", PartSpec("sparse_moe_swiglu", dict(
