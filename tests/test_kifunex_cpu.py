@@ -101,7 +101,7 @@ def test_parts_a_file_leaves_out_are_switched_off():
 
 
 @pytest.mark.parametrize("rot", [{"dims": 16, "base": 10000.0, "scaling": SCALING},
-                                 {"dims": 64, "base": 250000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}},
+                                 {"dims": 80, "base": 120000.0, "scaling": {"factor": 6.0, "low": 1.5, "high": 5.0, "original": 300}},
                                  {"dims": 32, "base": 500.0, "scaling": {"factor": 2.0, "low": 2.0, "high": 3.0, "original": 40}},
                                  {"dims": 48, "base": 500.0, "scaling": None}])
 def test_rotary_frequencies(rot):

@@ -215,7 +215,7 @@ def test_dynamic_tanh_as_an_ordinary_norm():
 def test_scaled_and_capped_logits():
     from nano_vllm_cpp_b200.csrc import ops
     z = torch.randn(5, 77, generator=torch.Generator().manual_seed(12), dtype=F64) * 20
-    for scale, cap in ((2.0, 15.0), (0.5, 0.0), (1.0, 3.0)):
+    for scale, cap in ((1.7, 11.0), (0.5, 0.0), (1.0, 3.0)):
         got = z.float().to(DEV)
         ops.scale_softcap(got, scale, cap)
         close(got, cap * torch.tanh(z * scale / cap) if cap > 0 else z * scale, 1e-6, f"scale {scale} cap {cap}")
@@ -282,7 +282,7 @@ def inputs(width, lengths, seed):
 
 MIXERS = [pk.attention_layer(dim=32, heads=4, kv_heads=2, window=24, rot_dims=16, scaling=SCALING, scale=0.2)["mixer"],
           pk.attention_layer(dim=48, heads=3, kv_heads=3, window=17, rot_dims=48, base=500.0, scale=0.11)["mixer"],
-          pk.attention_layer(dim=64, heads=8, kv_heads=1, window=40, rot_dims=0, scale=0.125)["mixer"],
+          pk.attention_layer(dim=64, heads=8, kv_heads=1, window=44, rot_dims=0, scale=0.125)["mixer"],
           pk.attention_layer(dim=40, heads=2, kv_heads=1, window=1, rot_dims=20, scale=0.3)["mixer"],
           pk.attention_layer(dim=128, heads=2, kv_heads=2, window=64, rot_dims=64, scale=0.09)["mixer"],
           pk.attention_layer(dim=64, heads=20, kv_heads=1, window=30, rot_dims=32, scale=0.12)["mixer"],
