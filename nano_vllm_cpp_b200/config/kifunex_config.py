@@ -16,7 +16,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Optional
 
-from .bizodra_config import _need, _positive
+from .fields import need as _need, positive as _positive
 from .model_config import ConfigError
 
 ARCHITECTURE = "Kifunex"
